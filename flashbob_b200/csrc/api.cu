@@ -1,0 +1,272 @@
+// Host side of the C ABI: argument checks, tensor-map construction and kernel dispatch.
+#include "../../include/bob_sm100.h"
+#include "sweep.cuh"
+#include "tmap.h"
+
+#include <cmath>
+#include <cstring>
+
+namespace bob {
+
+enum : int {
+    kErrNull = -1, kErrGeom = -2, kErrDtype = -3, kErrHeadDim = -4, kErrStride = -5,
+    kErrWorkspace = -6, kErrDevice = -7, kErrLaunch = -8, kErrAttr = -9, kErrAlign = -10,
+    kErrNoDriver = -100,
+};
+
+static constexpr size_t kStatusBlock = 256;
+
+static size_t round256(size_t x) { return (x + 255) / 256 * 256; }
+
+static int check_geom(const bob_sm100_geom* g) {
+    if (!g) return kErrNull;
+    if (g->B <= 0 || g->Hq <= 0 || g->Hkv <= 0 || g->Nq <= 0 || g->Nk <= 0 || g->D <= 0) return kErrGeom;
+    if (g->Hq % g->Hkv) return kErrGeom;
+    if (g->B > 65535 || g->Hq > 65535) return kErrGeom;
+    if (g->dtype != BOB_SM100_FP16 && g->dtype != BOB_SM100_BF16) return kErrDtype;
+    if (g->D % 16 || g->D > 128) return kErrHeadDim;
+    if (g->window < 0 || (g->window > 0 && !g->is_causal)) return kErrGeom;
+    if (g->q_offset < 0 || g->k_offset < 0) return kErrGeom;
+    if (!(g->scale > 0.f) || !std::isfinite(g->scale)) return kErrGeom;
+    return 0;
+}
+
+static int check_strides(const int64_t* s, const void* ptr) {
+    if (reinterpret_cast<uintptr_t>(ptr) % 16) return kErrAlign;
+    for (int i = 0; i < 3; ++i)
+        if (s[i] < 0 || s[i] % 8) return kErrStride;
+    return 0;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+        changed = prev != dev;
+    }
+    ~DeviceGuard() { if (changed && prev >= 0) cudaSetDevice(prev); }
+    bool changed = false;
+};
+
+struct TensorArg {
+    const void* ptr;
+    const int64_t* strides;   // batch, head, row
+    bool q_side;              // [B, Hq, Nq, D] (true) or [B, Hkv, Nk, D] (false)
+};
+
+template <int MODE, int DPAD, int TN, bool BF16>
+static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
+                        cudaStream_t stream) {
+    using CFG = SweepConfig<MODE, DPAD, TN>;
+    using MT = ModeTraits<MODE>;
+    auto build = [&](int t, int box_rows) -> int {
+        const TensorArg& a = tensors[t];
+        if (!a.ptr) return 0;
+        int rc = check_strides(a.strides, a.ptr);
+        if (rc) return rc;
+        return make_tile_map(&prm.map[t], a.ptr, BF16, g->D, a.q_side ? g->Nq : g->Nk,
+                             a.q_side ? g->Hq : g->Hkv, g->B, a.strides[2], a.strides[1],
+                             a.strides[0], box_rows);
+    };
+    for (int i = 0; i < MT::NOWN; ++i) {
+        int rc = build(own_tensor<MODE>(i), 128);
+        if (rc) return rc;
+    }
+    for (int i = 0; i < MT::NOTH; ++i) {
+        int rc = build(other_tensor<MODE>(i), TN);
+        if (rc) return rc;
+    }
+    auto kernel = sweep_kernel<MODE, DPAD, TN, BF16>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CFG::SMEM_BYTES) !=
+        cudaSuccess)
+        return kErrAttr;
+    const int n_own = MT::COL ? g->Nk : g->Nq;
+    dim3 grid((n_own + 127) / 128, MT::COL ? g->Hkv : g->Hq, g->B);
+    kernel<<<grid, CFG::NTHREADS, CFG::SMEM_BYTES, stream>>>(prm);
+    return cudaGetLastError() == cudaSuccess ? 0 : kErrLaunch;
+}
+
+// Tile width of the swept side per stage and head dimension: the widest that fits tensor memory
+// (512 columns) and shared memory (227 KB).
+template <int MODE, bool BF16>
+static int dispatch(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
+                    cudaStream_t stream) {
+    if (g->D <= 64) return launch_sweep<MODE, 64, 64, BF16>(g, prm, tensors, stream);
+    if constexpr (MODE == kBwd2Row || MODE == kBwd2Col)
+        return launch_sweep<MODE, 128, 32, BF16>(g, prm, tensors, stream);
+    else
+        return launch_sweep<MODE, 128, 64, BF16>(g, prm, tensors, stream);
+}
+
+template <int MODE>
+static int dispatch_dtype(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
+                          cudaStream_t stream) {
+    return g->dtype == BOB_SM100_BF16 ? dispatch<MODE, true>(g, prm, tensors, stream)
+                                      : dispatch<MODE, false>(g, prm, tensors, stream);
+}
+
+static void fill_common(const bob_sm100_geom* g, SweepParams& p, void* workspace) {
+    std::memset(&p, 0, sizeof(p));
+    p.B = g->B; p.Hq = g->Hq; p.Hkv = g->Hkv; p.G = g->Hq / g->Hkv; p.Nq = g->Nq; p.Nk = g->Nk;
+    p.D = g->D;
+    p.is_causal = g->is_causal ? 1 : 0;
+    p.window = g->window;
+    p.delta_off = g->q_offset - g->k_offset;
+    p.scale = g->scale;
+    p.status = static_cast<int*>(workspace);
+}
+
+static void set_strided(const void*& dst, long long& sb, long long& sh, long long& sn,
+                        const void* ptr, const int64_t* s) {
+    dst = ptr; sb = s[0]; sh = s[1]; sn = s[2];
+}
+
+}  // namespace bob
+
+using namespace bob;
+
+extern "C" int bob_sm100_version(void) { return 100; }
+
+extern "C" const char* bob_sm100_error_string(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case kErrNull: return "null pointer argument";
+        case kErrGeom: return "invalid geometry (sizes, heads, window, offsets or scale)";
+        case kErrDtype: return "dtype must be fp16 (0) or bf16 (1)";
+        case kErrHeadDim: return "head dimension must be a multiple of 16, at most 128";
+        case kErrStride: return "tensor strides must be non-negative multiples of 8 elements";
+        case kErrWorkspace: return "workspace missing or misaligned";
+        case kErrDevice: return "cannot select the device";
+        case kErrLaunch: return "kernel launch failed";
+        case kErrAttr: return "cannot raise the dynamic shared memory limit";
+        case kErrAlign: return "tensor base address must be 16-byte aligned";
+        case kErrNoDriver: return "cuTensorMapEncodeTiled is unavailable in this driver";
+        case -101: return "tensor base address must be 16-byte aligned";
+        case -102: return "tensor strides unusable for TMA";
+        case kStatusTimeoutLoad: return "device: a wait for a TMA load ran out";
+        case kStatusTimeoutMma: return "device: a wait in the MMA issuer ran out";
+        case kStatusTimeoutPw: return "device: a wait in the pointwise threads ran out";
+        default: return code < -1000 ? "cuTensorMapEncodeTiled failed" : "unknown code";
+    }
+}
+
+extern "C" size_t bob_sm100_workspace_bytes(int stage, const bob_sm100_geom* g) {
+    if (!g) return 0;
+    size_t bytes = kStatusBlock;
+    if (stage == BOB_SM100_STAGE_BWD2)
+        bytes += 2 * round256(static_cast<size_t>(g->B) * g->Hq * g->Nq * sizeof(float));
+    return bytes;
+}
+
+extern "C" int bob_sm100_read_status(const void* workspace, void* stream) {
+    if (!workspace) return kErrNull;
+    int v = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&v, workspace, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+        return kErrLaunch;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return kErrLaunch;
+    return v;
+}
+
+extern "C" int bob_sm100_fwd(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
+                             void* out, float* lse, void* workspace, void* stream) {
+    int rc = check_geom(g);
+    if (rc) return rc;
+    if (!q || !k || !v || !out || !lse) return kErrNull;
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256) return kErrWorkspace;
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return kErrDevice;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(workspace, 0, sizeof(int), s) != cudaSuccess) return kErrLaunch;
+
+    SweepParams p;
+    fill_common(g, p, workspace);
+    p.lse = lse;
+    p.res0 = out;
+    TensorArg t[kNumTensors] = {};
+    t[kTQ] = {q, g->q_strides, true};
+    t[kTK] = {k, g->k_strides, false};
+    t[kTV] = {v, g->v_strides, false};
+    return dispatch_dtype<kFwd>(g, p, t, s);
+}
+
+extern "C" int bob_sm100_bwd1(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
+                              const void* out, const float* lse, const void* dO, void* dQ, void* dK,
+                              void* dV, float* delta, void* workspace, void* stream) {
+    int rc = check_geom(g);
+    if (rc) return rc;
+    if (!q || !k || !v || !out || !lse || !dO || !dQ || !dK || !dV || !delta) return kErrNull;
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256) return kErrWorkspace;
+    if ((rc = check_strides(g->out_strides, out))) return rc;
+    if ((rc = check_strides(g->do_strides, dO))) return rc;
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return kErrDevice;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(workspace, 0, sizeof(int), s) != cudaSuccess) return kErrLaunch;
+
+    TensorArg t[kNumTensors] = {};
+    t[kTQ] = {q, g->q_strides, true};
+    t[kTK] = {k, g->k_strides, false};
+    t[kTV] = {v, g->v_strides, false};
+    t[kTDO] = {dO, g->do_strides, true};
+
+    SweepParams p;
+    fill_common(g, p, workspace);
+    p.lse = const_cast<float*>(lse);
+    p.delta = delta;
+    set_strided(p.out, p.out_sb, p.out_sh, p.out_sn, out, g->out_strides);
+    set_strided(p.dO, p.dO_sb, p.dO_sh, p.dO_sn, dO, g->do_strides);
+    p.res0 = dQ;
+    rc = dispatch_dtype<kBwd1Row>(g, p, t, s);      // dQ and delta
+    if (rc) return rc;
+    p.res0 = dK;
+    p.res1 = dV;
+    return dispatch_dtype<kBwd1Col>(g, p, t, s);    // dK and dV (reads delta)
+}
+
+extern "C" int bob_sm100_bwd2(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
+                              const void* out, const float* lse, const float* delta, const void* dO,
+                              const void* dQ, const void* uQ, const void* uK, const void* uV,
+                              void* Qbar, void* Kbar, void* Vbar, void* dObar, void* workspace,
+                              void* stream) {
+    int rc = check_geom(g);
+    if (rc) return rc;
+    if (!q || !k || !v || !out || !lse || !delta || !dO || !dQ || !Qbar || !Kbar || !Vbar || !dObar)
+        return kErrNull;
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256) return kErrWorkspace;
+    if ((rc = check_strides(g->out_strides, out))) return rc;
+    if ((rc = check_strides(g->dq_strides, dQ))) return rc;
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return kErrDevice;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(workspace, 0, sizeof(int), s) != cudaSuccess) return kErrLaunch;
+
+    TensorArg t[kNumTensors] = {};
+    t[kTQ] = {q, g->q_strides, true};
+    t[kTK] = {k, g->k_strides, false};
+    t[kTV] = {v, g->v_strides, false};
+    t[kTDO] = {dO, g->do_strides, true};
+    t[kTUQ] = {uQ, g->uq_strides, true};
+    t[kTUK] = {uK, g->uk_strides, false};
+    t[kTUV] = {uV, g->uv_strides, false};
+
+    SweepParams p;
+    fill_common(g, p, workspace);
+    p.has_uq = uQ != nullptr; p.has_uk = uK != nullptr; p.has_uv = uV != nullptr;
+    p.lse = const_cast<float*>(lse);
+    p.delta = const_cast<float*>(delta);
+    const size_t stat_bytes = round256(static_cast<size_t>(g->B) * g->Hq * g->Nq * sizeof(float));
+    p.alpha = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBlock);
+    p.ecirc = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBlock + stat_bytes);
+    set_strided(p.out, p.out_sb, p.out_sh, p.out_sn, out, g->out_strides);
+    set_strided(p.dQ, p.dQ_sb, p.dQ_sh, p.dQ_sn, dQ, g->dq_strides);
+    p.res0 = Qbar;
+    p.res1 = dObar;
+    rc = dispatch_dtype<kBwd2Row>(g, p, t, s);      // Qbar, dObar, alpha, ecirc
+    if (rc) return rc;
+    p.res0 = Kbar;
+    p.res1 = Vbar;
+    return dispatch_dtype<kBwd2Col>(g, p, t, s);    // Kbar, Vbar (reads alpha, ecirc)
+}
