@@ -4,6 +4,7 @@
 #include "tmap.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace bob {
@@ -116,6 +117,16 @@ static void fill_common(const bob_sm100_geom* g, SweepParams& p, void* workspace
     p.delta_off = g->q_offset - g->k_offset;
     p.scale = g->scale;
     p.status = static_cast<int*>(workspace);
+}
+
+// Profiling aid: BOB_SM100_BWD2_KERNELS=row or =col launches only that kernel of the second
+// backward (the column-owned kernel then reads whatever alpha / ecirc the workspace holds).
+static int bwd2_kernel_mask() {
+    const char* e = std::getenv("BOB_SM100_BWD2_KERNELS");
+    if (!e) return 3;
+    if (!std::strcmp(e, "row")) return 1;
+    if (!std::strcmp(e, "col")) return 2;
+    return 3;
 }
 
 static void set_strided(const void*& dst, long long& sb, long long& sh, long long& sn,
@@ -262,11 +273,17 @@ extern "C" int bob_sm100_bwd2(const bob_sm100_geom* g, const void* q, const void
     p.ecirc = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBlock + stat_bytes);
     set_strided(p.out, p.out_sb, p.out_sh, p.out_sn, out, g->out_strides);
     set_strided(p.dQ, p.dQ_sb, p.dQ_sh, p.dQ_sn, dQ, g->dq_strides);
-    p.res0 = Qbar;
-    p.res1 = dObar;
-    rc = dispatch_dtype<kBwd2Row>(g, p, t, s);      // Qbar, dObar, alpha, ecirc
-    if (rc) return rc;
-    p.res0 = Kbar;
-    p.res1 = Vbar;
-    return dispatch_dtype<kBwd2Col>(g, p, t, s);    // Kbar, Vbar (reads alpha, ecirc)
+    const int mask = bwd2_kernel_mask();
+    if (mask & 1) {
+        p.res0 = Qbar;
+        p.res1 = dObar;
+        rc = dispatch_dtype<kBwd2Row>(g, p, t, s);  // Qbar, dObar, alpha, ecirc
+        if (rc) return rc;
+    }
+    if (mask & 2) {
+        p.res0 = Kbar;
+        p.res1 = Vbar;
+        rc = dispatch_dtype<kBwd2Col>(g, p, t, s);  // Kbar, Vbar (reads alpha, ecirc)
+    }
+    return rc;
 }

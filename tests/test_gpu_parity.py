@@ -1,0 +1,200 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the fp64 CPU oracle.
+
+Tolerances.  The kernels round the same quantities to 16 bits as the reference's CUDA route does
+(derived operands, saved `out` and first-order `dQ`), so every output carries a relative L2 error
+of a few 1e-3 in bf16 (a few 1e-4 in fp16) against fp64.  Bars used here, per output tensor:
+bf16  l2_rel <= 6e-3, max_abs <= 2e-2 * max|ref|;  fp16  l2_rel <= 1e-3, max_abs <= 4e-3 * max|ref|;
+and the reference's own acceptance test, assert_close(rtol=atol=0.08)
+(reference: tests/cuda/test_attention_correctness.py:53).
+"""
+
+import ast
+import ctypes
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from flashbob_b200 import _lib, ops
+from oracle import bob_oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).parent / "golden"
+BF16, FP16 = torch.bfloat16, torch.float16
+BARS = {BF16: (6e-3, 2e-2), FP16: (1e-3, 4e-3)}
+
+
+def _check(name, got, ref, dtype):
+    m = O.error_metrics(got, ref)
+    l2, mx = BARS[dtype]
+    assert torch.isfinite(got.float()).all(), name
+    assert m["l2_rel"] <= l2, (name, m)
+    assert m["max_abs_rel"] <= mx, (name, m)
+    torch.testing.assert_close(got.double().cpu(), ref.double(), rtol=0.08, atol=0.08)
+
+
+def _run_kernels(q, k, v, dO, uQ, uK, uV, geom):
+    c = lambda t: None if t is None else t.cuda()
+    qd, kd, vd, dOd, uQd, uKd, uVd = map(c, (q, k, v, dO, uQ, uK, uV))
+    out, lse = ops.attention_forward(qd, kd, vd, **geom)
+    dQ, dK, dV, delta = ops.attention_first_backward(qd, kd, vd, out, lse, dOd, **geom)
+    Qb, Kb, Vb, dOb = ops.attention_second_backward(qd, kd, vd, out, lse, delta, dOd, dQ, uQd, uKd,
+                                                    uVd, **geom)
+    return dict(out=out, dQ=dQ, dK=dK, dV=dV, Qbar=Qb, Kbar=Kb, Vbar=Vb, dObar=dOb), lse, delta
+
+
+def _geom(Nq, Nk, **kw):
+    causal = kw.get("is_causal", False)
+    return dict(is_causal=causal, window_size=kw.get("window_size", 0),
+                q_offset=O.infer_q_offset(Nq, Nk, kw.get("q_offset"), kw.get("k_offset", 0), causal),
+                k_offset=kw.get("k_offset", 0), scale=kw.get("scale"))
+
+
+def test_tensor_core_plumbing_known_answer():
+    lib = _lib.load()
+    for dtype in (BF16, FP16):
+        g = torch.Generator().manual_seed(0)
+        a = torch.randn(128, 64, generator=g).to(dtype).cuda()
+        b = torch.randn(64, 64, generator=g).to(dtype).cuda()
+        out = torch.zeros(3, 128, 64, device="cuda")
+        st = torch.zeros(1, dtype=torch.int32, device="cuda")
+        rc = lib.bob_sm100_selftest(a.data_ptr(), b.data_ptr(), int(dtype == BF16), out.data_ptr(),
+                                    st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert rc == 0 and st.item() == 0
+        ab_t, ab = a.double() @ b.double().T, a.double() @ b.double()
+        torch.testing.assert_close(out[0].double(), ab_t, rtol=1e-5, atol=1e-4)
+        torch.testing.assert_close(out[1].double(), ab, rtol=1e-5, atol=1e-4)
+        torch.testing.assert_close(out[2].double(), ab_t, rtol=1e-5, atol=1e-4)
+
+
+CASES = {
+    # name: (B, Hq, Hkv, Nq, Nk, D, dtype, kwargs)
+    "causal64": (1, 2, 2, 64, 64, 64, BF16, dict(is_causal=True)),
+    "noncausal48_d128": (1, 2, 2, 48, 48, 128, BF16, dict()),
+    "window16": (1, 2, 2, 64, 64, 64, BF16, dict(is_causal=True, window_size=16)),
+    "gqa": (1, 8, 2, 64, 64, 64, BF16, dict(is_causal=True)),
+    "mqa": (1, 8, 1, 64, 64, 64, BF16, dict(is_causal=True)),
+    "rect_w32": (1, 2, 2, 32, 64, 64, BF16, dict(is_causal=True, window_size=32, q_offset=32, k_offset=0)),
+    "ragged_causal": (2, 3, 3, 301, 301, 64, BF16, dict(is_causal=True, scale=0.2)),
+    "ragged_noncausal_rect": (1, 2, 2, 77, 203, 64, BF16, dict()),
+    "window_long": (1, 2, 2, 700, 700, 64, BF16, dict(is_causal=True, window_size=130)),
+    "gqa_ragged": (2, 6, 2, 333, 333, 64, BF16, dict(is_causal=True)),
+    "d32": (1, 2, 2, 100, 100, 32, BF16, dict(is_causal=True)),
+    "d128_causal": (1, 2, 2, 384, 384, 128, BF16, dict(is_causal=True)),
+    "d128_gqa": (1, 4, 1, 260, 260, 128, BF16, dict(is_causal=True)),
+    "fp16_causal": (1, 2, 2, 200, 200, 64, FP16, dict(is_causal=True)),
+    "fp16_rect_d128": (2, 3, 3, 128, 512, 128, FP16, dict(is_causal=True, window_size=256)),
+    "large_offsets": (1, 2, 2, 128, 512, 64, BF16, dict(is_causal=True, window_size=256, q_offset=1000, k_offset=616)),
+    "tiny": (1, 1, 1, 1, 1, 32, BF16, dict(is_causal=True)),
+    "one_query_many_keys": (1, 2, 2, 1, 500, 64, BF16, dict(is_causal=True)),
+    "keyless_rows": (1, 2, 2, 96, 64, 64, BF16, dict(is_causal=True, q_offset=0, k_offset=40)),
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_all_eight_outputs_match_oracle(name):
+    B, Hq, Hkv, Nq, Nk, D, dtype, kw = CASES[name]
+    q, k, v, dO, uQ = O.seeded_inputs(11, (B, Hq, Nq, D), (B, Hkv, Nk, D), dtype, n_extra_q=2)
+    uK, uV = O.seeded_inputs(12, (B, Hq, Nq, D), (B, Hkv, Nk, D), dtype)[1:]
+    geom = _geom(Nq, Nk, **kw)
+    ref = O.bob_closed_form(q, k, v, dO, uQ, uK, uV, **geom)
+    got, lse, delta = _run_kernels(q, k, v, dO, uQ, uK, uV, geom)
+    fin = torch.isfinite(ref.lse)
+    assert torch.equal(torch.isfinite(lse.cpu()), fin)
+    torch.testing.assert_close(lse.cpu().double()[fin], ref.lse[fin], rtol=1e-5, atol=1e-5)
+    for n in O.OUTPUT_NAMES:
+        _check(f"{name}:{n}", got[n], getattr(ref, n), dtype)
+
+
+@pytest.mark.parametrize("missing", [("k", "v"), ("q",), ("q", "k"), ("v",), ("q", "v")])
+def test_undefined_tangents(missing):
+    """Undefined tangents switch products off; results equal the oracle with those tangents zero
+    (reference: tests/cuda/test_attention_correctness.py:56-76, src/bob/sdpa.py:177-180)."""
+    B, Hq, Hkv, Nq, Nk, D = 1, 4, 2, 150, 150, 64
+    q, k, v, dO, uQ = O.seeded_inputs(21, (B, Hq, Nq, D), (B, Hkv, Nk, D), BF16, n_extra_q=2)
+    uK, uV = O.seeded_inputs(22, (B, Hq, Nq, D), (B, Hkv, Nk, D), BF16)[1:]
+    uQ = None if "q" in missing else uQ
+    uK = None if "k" in missing else uK
+    uV = None if "v" in missing else uV
+    geom = _geom(Nq, Nk, is_causal=True)
+    ref = O.bob_closed_form(q, k, v, dO, uQ, uK, uV, **geom)
+    got, _, _ = _run_kernels(q, k, v, dO, uQ, uK, uV, geom)
+    for n in ("Qbar", "Kbar", "Vbar", "dObar"):
+        r = getattr(ref, n)
+        if r.abs().max() == 0:
+            assert got[n].float().abs().max().item() == 0, n
+        else:
+            _check(f"{missing}:{n}", got[n], r, BF16)
+
+
+@pytest.mark.parametrize("name", ["causal", "noncausal", "window", "gqa", "mqa", "rect"])
+def test_golden_geometries_of_the_reference_cuda_tests(name):
+    """Shapes and seeds of the reference's CUDA acceptance test, inputs rounded to bf16."""
+    z = np.load(GOLDEN / f"{name}.npz", allow_pickle=True)
+    meta = ast.literal_eval(str(z["meta"]))
+    q_shape = (1, meta["hq"], meta["nq"], meta["d"])
+    kv_shape = (1, meta["hkv"], meta["nk"], meta["d"])
+    g = torch.Generator().manual_seed(meta["seed"])
+    r = lambda s: torch.randn(s, dtype=torch.float32, generator=g).to(BF16)
+    q, k, v, dO, uQ, uK, uV = r(q_shape), r(kv_shape), r(kv_shape), r(q_shape), r(q_shape), r(kv_shape), r(kv_shape)
+    geom = _geom(meta["nq"], meta["nk"], **meta["kw"])
+    got, _, _ = _run_kernels(q, k, v, dO, uQ, uK, uV, geom)
+    ref = O.bob_closed_form(q, k, v, dO, uQ, uK, uV, **geom)
+    for n in O.OUTPUT_NAMES:
+        _check(f"{name}:{n}", got[n], getattr(ref, n), BF16)
+        # the unrounded fp64 golden differs only by input rounding: loose sanity bound
+        gold = torch.from_numpy(z[f"ref64_{n}"])
+        assert O.error_metrics(got[n], gold)["l2_rel"] < 0.05, n
+
+
+def test_strided_inputs_are_read_in_place():
+    """[B, N, H, D] storage viewed as [B, H, N, D] goes to the kernels without a copy."""
+    B, H, N, D = 2, 4, 160, 64
+    q, k, v, dO, uQ = O.seeded_inputs(31, (B, H, N, D), (B, H, N, D), BF16, n_extra_q=2)
+    uK, uV = O.seeded_inputs(32, (B, H, N, D), (B, H, N, D), BF16)[1:]
+    geom = _geom(N, N, is_causal=True)
+    ref = O.bob_closed_form(q, k, v, dO, uQ, uK, uV, **geom)
+    tr = lambda t: t.cuda().transpose(1, 2).contiguous().transpose(1, 2)   # same values, BNHD storage
+    qd, kd, vd, dOd, uQd, uKd, uVd = map(tr, (q, k, v, dO, uQ, uK, uV))
+    assert not qd.is_contiguous() and ops._tma_ready(qd) is qd
+    out, lse = ops.attention_forward(qd, kd, vd, **geom)
+    dQ, dK, dV, delta = ops.attention_first_backward(qd, kd, vd, out, lse, dOd, **geom)
+    res = ops.attention_second_backward(qd, kd, vd, out, lse, delta, dOd, dQ, uQd, uKd, uVd, **geom)
+    for n, t in zip(O.OUTPUT_NAMES, (out, dQ, dK, dV, *res)):
+        _check(f"strided:{n}", t, getattr(ref, n), BF16)
+    # a layout the kernels cannot address (odd row stride) is copied, not rejected
+    odd = torch.randn(B, H, N, D + 1, device="cuda").to(BF16)[..., :D]
+    assert ops._tma_ready(odd) is not odd
+
+
+def test_c_abi_rejects_bad_arguments_on_the_host():
+    lib = _lib.load()
+    g = _lib.Geom()
+    g.B, g.Hq, g.Hkv, g.Nq, g.Nk, g.D = 1, 2, 2, 64, 64, 64
+    g.dtype, g.is_causal, g.window, g.device, g.scale = _lib.BF16, 1, 0, 0, 0.125
+    for f in (g.q_strides, g.k_strides, g.v_strides):
+        f[0], f[1], f[2] = 2 * 64 * 64, 64 * 64, 64
+    t = torch.zeros(1, 2, 64, 64, dtype=BF16, device="cuda")
+    lse = torch.zeros(1, 2, 64, device="cuda")
+    ws = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    vp = lambda x: ctypes.c_void_p(x.data_ptr())
+    call = lambda: lib.bob_sm100_fwd(ctypes.byref(g), vp(t), vp(t), vp(t), vp(t), vp(lse), vp(ws), None)
+    assert call() == 0
+    assert lib.bob_sm100_fwd(ctypes.byref(g), None, vp(t), vp(t), vp(t), vp(lse), vp(ws), None) == -1
+    g.D = 72
+    assert call() == -4
+    g.D = 64
+    g.Hkv = 3
+    assert call() == -2
+    g.Hkv = 2
+    g.window, g.is_causal = 4, 0
+    assert call() == -2
+    g.window, g.is_causal = 0, 1
+    g.q_strides[2] = 65
+    assert call() == -5
+    g.q_strides[2] = 64
+    assert lib.bob_sm100_fwd(ctypes.byref(g), vp(t), vp(t), vp(t), vp(t), vp(lse), None, None) == -6
+    torch.cuda.synchronize()
+    assert b"stride" in lib.bob_sm100_error_string(-5)
