@@ -23,7 +23,7 @@ static int check_geom(const bob_sm100_geom* g) {
     if (!g) return kErrNull;
     if (g->B <= 0 || g->Hq <= 0 || g->Hkv <= 0 || g->Nq <= 0 || g->Nk <= 0 || g->D <= 0) return kErrGeom;
     if (g->Hq % g->Hkv) return kErrGeom;
-    if (g->B > 65535 || g->Hq > 65535) return kErrGeom;
+    if (g->Nq > (1 << 28) || g->Nk > (1 << 28)) return kErrGeom;
     if (g->dtype != BOB_SM100_FP16 && g->dtype != BOB_SM100_BF16) return kErrDtype;
     if (g->D % 16 || g->D > 128) return kErrHeadDim;
     if (g->window < 0 || (g->window > 0 && !g->is_causal)) return kErrGeom;
@@ -84,7 +84,9 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
         cudaSuccess)
         return kErrAttr;
     const int n_own = MT::COL ? g->Nk : g->Nq;
-    dim3 grid((n_own + 127) / 128, MT::COL ? g->Hkv : g->Hq, g->B);
+    const long long ctas = (long long)((n_own + 127) / 128) * (MT::COL ? g->Hkv : g->Hq) * g->B;
+    if (ctas > 0x7fffffffLL) return kErrGeom;
+    dim3 grid((unsigned)ctas, 1, 1);
     kernel<<<grid, CFG::NTHREADS, CFG::SMEM_BYTES, stream>>>(prm);
     return cudaGetLastError() == cudaSuccess ? 0 : kErrLaunch;
 }
@@ -114,7 +116,10 @@ static void fill_common(const bob_sm100_geom* g, SweepParams& p, void* workspace
     p.D = g->D;
     p.is_causal = g->is_causal ? 1 : 0;
     p.window = g->window;
-    p.delta_off = g->q_offset - g->k_offset;
+    // Beyond +-2^30 every pair is masked the same way as at the bound (sequence lengths are far
+    // smaller), and 32-bit position arithmetic in the kernels cannot overflow.
+    const int64_t d = g->q_offset - g->k_offset;
+    p.delta_off = static_cast<int>(d > (1 << 30) ? (1 << 30) : (d < -(1 << 30) ? -(1 << 30) : d));
     p.scale = g->scale;
     p.status = static_cast<int*>(workspace);
 }

@@ -129,6 +129,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Each thread of the warp reads 8 consecutive fp32 columns of its own lane.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+    uint32_t r[8];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // ----------------------------------------------------------------------------------------
 // UMMA descriptors
 // ----------------------------------------------------------------------------------------
@@ -140,10 +152,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 // `addr` = tile base (1024-byte aligned) + the K offset of this instruction:
 //   K-major : + 32 bytes per 16-element K step (stays inside the 128-byte swizzle span)
 //   MN-major: + 2048 bytes per 16-row K step.
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr) {
+// `lbo_bytes` matters only for an MN-major operand wider than 64 elements: it is the distance
+// from the tile holding elements 0..63 of the M/N index to the tile holding elements 64..127.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr, uint32_t lbo_bytes = 16) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);       // start address, 16-byte units
-    d |= static_cast<uint64_t>(1) << 16;                    // leading byte offset (unused: one span)
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;   // leading byte offset
     d |= static_cast<uint64_t>(1024 >> 4) << 32;            // stride byte offset: 8-row group pitch
     d |= static_cast<uint64_t>(1) << 46;                    // descriptor version (Blackwell)
     d |= static_cast<uint64_t>(2) << 61;                    // SWIZZLE_128B

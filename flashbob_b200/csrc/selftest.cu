@@ -3,6 +3,9 @@
 //   out[0] = A * B^T   A, B staged by TMA; B read K-major   (score-shaped products)
 //   out[1] = A * B     B read MN-major from the same tile   (output-shaped products)
 //   out[2] = A'* B^T   A' written to swizzled shared memory by threads (derived operands)
+//   out[3], out[4] = A * [B; B]^T  one N=128 K-major product over two adjacent B tiles
+//   out[5], out[6] = A * [B | B]   one N=128 MN-major product whose second 64 columns come from a
+//                                  tile `leading byte offset` away (merged output products)
 // A is [128, 64], B is [64, 64], both fp16 or both bf16 (kind::f16 needs one format for A and B).
 #include "ptx.cuh"
 #include "tmap.h"
@@ -21,7 +24,8 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t tile_a = base;                 // 128 rows x 128 B
     const uint32_t tile_b = base + 16384;         // 64 rows x 128 B
-    const uint32_t tile_a2 = base + 16384 + 8192; // 128 rows x 128 B
+    const uint32_t tile_b2 = base + 16384 + 8192; // second copy of B, directly after the first
+    const uint32_t tile_a2 = tile_b2 + 8192;      // 128 rows x 128 B
     const uint32_t bar_load = tile_a2 + 16384;
     const uint32_t bar_mma = bar_load + 8;
     const uint32_t tmem_slot = bar_load + 16;
@@ -36,7 +40,7 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
         mbar_fence_init();
     }
     if (warp == 0) {
-        tmem_alloc(tmem_slot, 256);
+        tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -45,9 +49,10 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
     const uint32_t tmem = *tmem_slot_ptr;
 
     if (tid == 0) {
-        mbar_arrive_expect_tx(bar_load, 16384 + 8192);
+        mbar_arrive_expect_tx(bar_load, 16384 + 2 * 8192);
         tma_load_4d(tile_a, &maps.a, bar_load, 0, 0, 0, 0);
         tma_load_4d(tile_b, &maps.b, bar_load, 0, 0, 0, 0);
+        tma_load_4d(tile_b2, &maps.b, bar_load, 0, 0, 0, 0);
     }
     // Threads restate A into the third tile with the swizzle formula.
     {
@@ -80,13 +85,25 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
             umma_ss(tmem + 128, umma_smem_desc(tile_a2 + ks * 32),
                     umma_smem_desc(tile_b + ks * 32), id_k, ks > 0);
         }
+        const uint32_t id_k128 = umma_idesc(fmt, fmt, 128, false);
+        const uint32_t id_mn128 = umma_idesc(fmt, fmt, 128, true);
+        #pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            umma_ss(tmem + 192, umma_smem_desc(tile_a + ks * 32), umma_smem_desc(tile_b + ks * 32),
+                    id_k128, ks > 0);
+        }
+        #pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            umma_ss(tmem + 320, umma_smem_desc(tile_a + ks * 32),
+                    umma_smem_desc(tile_b + ks * 2048, tile_b2 - tile_b), id_mn128, ks > 0);
+        }
         umma_commit(bar_mma);
     }
     ok = ok && mbar_wait(bar_mma, 0);
     tc_fence_after_sync();
     if (ok) {
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-        for (int t = 0; t < 3; ++t) {
+        for (int t = 0; t < 7; ++t) {
             for (int c = 0; c < 64; c += 16) {
                 float v[16];
                 tmem_ld16(lane_base + t * 64 + c, v);
@@ -100,7 +117,7 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 }  // namespace bob
@@ -114,7 +131,7 @@ extern "C" int bob_sm100_selftest(const void* a, const void* b, int is_bf16, flo
     if (rc) return rc;
     rc = make_tile_map(&maps.b, b, is_bf16 != 0, 64, 64, 1, 1, 64, 64 * 64, 64 * 64, 64);
     if (rc) return rc;
-    const int smem = 16384 + 8192 + 16384 + 64 + 1024;
+    const int smem = 16384 + 2 * 8192 + 16384 + 64 + 1024;
     auto kernel = selftest_kernel;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)

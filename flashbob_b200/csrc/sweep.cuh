@@ -38,7 +38,7 @@ struct SweepParams {
     // geometry
     int B, Hq, Hkv, G, Nq, Nk, D;
     int is_causal, window;
-    long long delta_off;          // q_offset - k_offset
+    int delta_off;                // q_offset - k_offset, clamped to +-2^30
     float scale;
     int has_uq, has_uk, has_uv;   // 0 = that tangent is undefined (treated as zero, products skipped)
     // global tensors read with plain loads (element strides: batch, head, row; unit head-dim stride)
@@ -75,8 +75,8 @@ template <int MODE> __host__ __device__ constexpr int own_tensor(int i) {
 template <int MODE> __host__ __device__ constexpr int other_tensor(int i) {
     if (MODE == kFwd || MODE == kBwd1Row) return i == 0 ? kTK : kTV;
     if (MODE == kBwd1Col) return i == 0 ? kTQ : kTDO;
-    if (MODE == kBwd2Row) return i == 0 ? kTK : (i == 1 ? kTV : (i == 2 ? kTUK : kTUV));
-    return i == 0 ? kTQ : (i == 1 ? kTDO : kTUQ);
+    if (MODE == kBwd2Row) return i == 0 ? kTK : (i == 1 ? kTUK : (i == 2 ? kTV : kTUV));   // K, uK adjacent; V, uV adjacent
+    return i == 0 ? kTQ : (i == 1 ? kTUQ : kTDO);                                          // Q, uQ adjacent
 }
 
 template <int MODE, int DPAD, int TN>
@@ -88,7 +88,8 @@ struct SweepConfig {
     static constexpr int NSTAGE = 2;
     static constexpr int KSUB = DPAD / 64;                 // 64-element sub-tiles along the head dim
     static constexpr int OWN_TILE_BYTES = 128 * 128 * KSUB;
-    static constexpr int OTH_TILE_BYTES = TN * 128 * KSUB;
+    static constexpr int OTH_SUB_BYTES = TN * 128;         // one 64-element-wide sub-tile of a swept tensor
+    static constexpr int OTH_STAGE_BYTES = KSUB * MT::NOTH * OTH_SUB_BYTES;   // laid out [sub][slot]
     static constexpr int OPER_PER_TILE = 64 / TN;          // operands packed per 128-byte-row tile
     static constexpr int NOPER_TILES = (MT::NOPER + OPER_PER_TILE - 1) / OPER_PER_TILE;
     static constexpr int OPER_TILE_BYTES = 128 * 128;
@@ -100,7 +101,7 @@ struct SweepConfig {
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int OFF_OWN = 0;
     static constexpr int OFF_OTH = OFF_OWN + MT::NOWN * OWN_TILE_BYTES;
-    static constexpr int OFF_OPER = OFF_OTH + NSTAGE * MT::NOTH * OTH_TILE_BYTES;
+    static constexpr int OFF_OPER = OFF_OTH + NSTAGE * OTH_STAGE_BYTES;
     static constexpr int OFF_STAT = OFF_OPER + NOPER_TILES * OPER_TILE_BYTES;   // [2][4][TN] floats
     static constexpr int OFF_RED = OFF_STAT + 2 * 4 * TN * 4;                   // [4][NSPLIT][128] floats
     static constexpr int OFF_BAR = OFF_RED + 4 * NSPLIT * 128 * 4;
@@ -146,22 +147,8 @@ __device__ __forceinline__ void store16_from_float(void* base, long long elem_of
     p[0] = a; p[1] = b;
 }
 
-// Write 16 consecutive operand columns (starting at column `col0`, a multiple of 16, of a
-// 64-column tile) of row `row` into a swizzled operand tile.
-template <bool BF16>
-__device__ __forceinline__ void store_operand16(uint32_t tile, int row, int col0, const float* v) {
-    const uint32_t c = static_cast<uint32_t>(col0) >> 3;
-    st_shared_v4(tile + sw128_offset(row, c), pack2<BF16>(v[0], v[1]), pack2<BF16>(v[2], v[3]),
-                 pack2<BF16>(v[4], v[5]), pack2<BF16>(v[6], v[7]));
-    st_shared_v4(tile + sw128_offset(row, c + 1), pack2<BF16>(v[8], v[9]), pack2<BF16>(v[10], v[11]),
-                 pack2<BF16>(v[12], v[13]), pack2<BF16>(v[14], v[15]));
-}
-
-__device__ __forceinline__ void store_operand_words(uint32_t tile, int row, int col0, const uint32_t* w) {
-    const uint32_t c = static_cast<uint32_t>(col0) >> 3;
-    st_shared_v4(tile + sw128_offset(row, c), w[0], w[1], w[2], w[3]);
-    st_shared_v4(tile + sw128_offset(row, c + 1), w[4], w[5], w[6], w[7]);
-}
+template <bool V> struct BoolTag { static constexpr bool value = V; };
+template <int V> struct IntTag { static constexpr int value = V; };
 
 template <int MODE, int DPAD, int TN, bool BF16>
 __global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN>::NTHREADS, 1)
@@ -170,6 +157,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     using MT = ModeTraits<MODE>;
     constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
     constexpr bool COL = MT::COL;
+    constexpr bool BWD2 = (MODE == kBwd2Row || MODE == kBwd2Col);
     constexpr float kLog2e = 1.4426950408889634f;
     constexpr float kLn2 = 0.6931471805599453f;
 
@@ -196,32 +184,39 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     const int lane = tid & 31;
 
     // ---- which tile this CTA owns, and the range of tiles it sweeps --------------------------
+    // The grid is one-dimensional and ordered longest-sweep-first: all heads' heaviest tile, then
+    // all heads' second heaviest, ... so the tail of the launch consists of short sweeps.
     const int n_own = COL ? p.Nk : p.Nq;
     const int n_oth = COL ? p.Nq : p.Nk;
     const int n_own_tiles = (n_own + 127) / 128;
-    // Row-owned causal tiles get heavier with the row index: start the heavy ones first.
-    const int own_tile = (!COL && p.is_causal) ? (n_own_tiles - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+    const int grid_heads = COL ? p.Hkv : p.Hq;
+    const int per_rank = grid_heads * p.B;
+    const int tile_rank = (int)blockIdx.x / per_rank;
+    const int rem = (int)blockIdx.x % per_rank;
+    const int head = rem % grid_heads;           // query head (row-owned) or KV head (column-owned)
+    const int batch = rem / grid_heads;
+    // causal: row-owned sweeps grow with the row index, column-owned ones shrink with the column
+    const int own_tile = (!COL && p.is_causal) ? (n_own_tiles - 1 - tile_rank) : tile_rank;
     const int own0 = own_tile * 128;
-    const int head = blockIdx.y;                 // query head (row-owned) or KV head (column-owned)
-    const int batch = blockIdx.z;
     const int kv_head = COL ? head : head / p.G;
     const int n_outer = (MODE == kFwd) ? 2 : (COL ? p.G : 1);
+    const int doff = p.delta_off;                // q_offset - k_offset, clamped to +-2^30 by the host
 
-    long long lo = 0, hi = n_oth;                // other-side positions [lo, hi) that can be unmasked
+    int lo = 0, hi = n_oth;                      // other-side positions [lo, hi) that can be unmasked
     {
-        const long long own_last = (long long)min(own0 + 127, n_own - 1);
+        const int own_last = min(own0 + 127, n_own - 1);
         if (p.is_causal) {
             if (!COL) {
-                hi = min((long long)n_oth, own_last + p.delta_off + 1);
-                if (p.window > 0) lo = max(0LL, (long long)own0 + p.delta_off - p.window + 1);
+                hi = (int)min((long long)n_oth, (long long)own_last + doff + 1);
+                if (p.window > 0) lo = (int)max(0LL, (long long)own0 + doff - p.window + 1);
             } else {
-                lo = max(0LL, (long long)own0 - p.delta_off);
-                if (p.window > 0) hi = min((long long)n_oth, own_last - p.delta_off + p.window);
+                lo = (int)max(0LL, (long long)own0 - doff);
+                if (p.window > 0) hi = (int)min((long long)n_oth, (long long)own_last - doff + p.window);
             }
         }
     }
-    const int t_lo = (hi > lo) ? (int)(lo / TN) : 0;
-    const int t_hi = (hi > lo) ? (int)((hi + TN - 1) / TN) : 0;
+    const int t_lo = (hi > lo) ? lo / TN : 0;
+    const int t_hi = (hi > lo) ? (hi + TN - 1) / TN : 0;
     const int T = t_hi - t_lo;
     const int total = T * n_outer;
 
@@ -257,6 +252,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     auto has_tensor = [&](int t) {
         return t == kTUQ ? p.has_uq : (t == kTUK ? p.has_uk : (t == kTUV ? p.has_uv : 1));
     };
+    // shared-memory address of sub-tile `sub` of swept-tensor slot `slot` in pipeline stage `stage`
+    auto oth_addr = [&](int stage, int sub, int slot) {
+        return sbase + CFG::OFF_OTH + stage * CFG::OTH_STAGE_BYTES + (sub * MT::NOTH + slot) * CFG::OTH_SUB_BYTES;
+    };
 
     if (warp == NPW / 32 + 1) {
         // =========================== TMA producer =============================================
@@ -288,8 +287,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 uint32_t bytes = 0;
                 #pragma unroll
                 for (int i = 0; i < MT::NOTH; ++i) {
-                    if (MODE == kFwd && outer == 0 && i == 1) continue;
-                    if (has_tensor(other_tensor<MODE>(i))) bytes += CFG::OTH_TILE_BYTES;
+                    if (MODE == kFwd && outer == 0 && i == 1) continue;     // the statistics sweep needs K only
+                    if (has_tensor(other_tensor<MODE>(i))) bytes += KSUB * CFG::OTH_SUB_BYTES;
                 }
                 mbar_arrive_expect_tx(bar_full(s), bytes);
                 #pragma unroll
@@ -299,9 +298,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     if (!has_tensor(t)) continue;
                     #pragma unroll
                     for (int ks = 0; ks < KSUB; ++ks)
-                        tma_load_4d(sbase + CFG::OFF_OTH + (s * MT::NOTH + i) * CFG::OTH_TILE_BYTES +
-                                        ks * (TN * 128),
-                                    &p.map[t], bar_full(s), ks * 64, tile * TN, oth_head, batch);
+                        tma_load_4d(oth_addr(s, ks, i), &p.map[t], bar_full(s), ks * 64, tile * TN, oth_head, batch);
                 }
                 ++issued;
             }
@@ -314,37 +311,54 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         // =========================== MMA issuer ===============================================
         if (lane == 0 && total > 0) {
             constexpr uint32_t fmt = BF16 ? kFmtBF16 : kFmtF16;
-            constexpr uint32_t idesc_sc = umma_idesc(fmt, fmt, TN, false);
-            constexpr uint32_t idesc_out = umma_idesc(fmt, fmt, 64, true);
             const uint32_t own_base = sbase + CFG::OFF_OWN;
 
-            // score-shaped product: acc[128, TN] (+)= own[slot_a] * other[slot_b]^T
-            auto score_mma = [&](int acc, int slot_a, int slot_b, int stage, bool accumulate) {
+            // score-shaped product: acc[128, NS*TN] (+)= own[slot_a] * other[slot_b .. slot_b+NS-1]^T.
+            // NS = 2 takes two adjacent swept tiles as one 2*TN-row operand and fills two adjacent
+            // accumulators with one instruction per K step (the own tile is read once, not twice).
+            auto score_mma = [&](auto ns_tag, int acc, int slot_a, int slot_b, int stage, bool accumulate) {
+                constexpr int NS = decltype(ns_tag)::value;
+                constexpr uint32_t idesc = umma_idesc(fmt, fmt, NS * TN, false);
                 const uint32_t a = own_base + slot_a * CFG::OWN_TILE_BYTES;
-                const uint32_t b = sbase + CFG::OFF_OTH + (stage * MT::NOTH + slot_b) * CFG::OTH_TILE_BYTES;
                 #pragma unroll
                 for (int ks = 0; ks < DPAD / 16; ++ks) {
                     const uint32_t ao = (ks / 4) * (128 * 128) + (ks % 4) * 32;
-                    const uint32_t bo = (ks / 4) * (TN * 128) + (ks % 4) * 32;
-                    umma_ss(tmem + acc * TN, umma_smem_desc(a + ao), umma_smem_desc(b + bo), idesc_sc,
+                    const uint32_t b = oth_addr(stage, ks / 4, slot_b) + (ks % 4) * 32;
+                    umma_ss(tmem + acc * TN, umma_smem_desc(a + ao), umma_smem_desc(b), idesc,
                             (accumulate || ks > 0) ? 1u : 0u);
                 }
             };
             // output-shaped product: out[128, DPAD] (+)= operand[oper] * other[slot_b]
             auto out_mma = [&](int out, int oper, int slot_b, int stage, bool accumulate) {
+                constexpr uint32_t idesc = umma_idesc(fmt, fmt, 64, true);
                 const uint32_t a = sbase + CFG::OFF_OPER + (oper / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES +
                                    (oper % CFG::OPER_PER_TILE) * (TN * 2);
-                const uint32_t b = sbase + CFG::OFF_OTH + (stage * MT::NOTH + slot_b) * CFG::OTH_TILE_BYTES;
                 #pragma unroll
                 for (int db = 0; db < KSUB; ++db) {
                     #pragma unroll
                     for (int ks = 0; ks < TN / 16; ++ks) {
                         umma_ss(tmem_out + out * DPAD + db * 64, umma_smem_desc(a + ks * 32),
-                                umma_smem_desc(b + db * (TN * 128) + ks * 2048), idesc_out,
+                                umma_smem_desc(oth_addr(stage, db, slot_b) + ks * 2048), idesc,
                                 (accumulate || ks > 0) ? 1u : 0u);
                     }
                 }
             };
+            // two output-shaped products sharing the operand: (out, out+1)[128, 2*64] (+)=
+            // operand[oper] * (other[slot_b] | other[slot_b2]); head dim <= 64 only
+            auto out_mma_pair = [&](int out, int oper, int slot_b, int slot_b2, int stage, bool accumulate) {
+                constexpr uint32_t idesc = umma_idesc(fmt, fmt, 128, true);
+                const uint32_t a = sbase + CFG::OFF_OPER + (oper / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES +
+                                   (oper % CFG::OPER_PER_TILE) * (TN * 2);
+                const uint32_t lbo = (slot_b2 - slot_b) * CFG::OTH_SUB_BYTES;
+                #pragma unroll
+                for (int ks = 0; ks < TN / 16; ++ks) {
+                    umma_ss(tmem_out + out * DPAD, umma_smem_desc(a + ks * 32),
+                            umma_smem_desc(oth_addr(stage, 0, slot_b) + ks * 2048, lbo), idesc,
+                            (accumulate || ks > 0) ? 1u : 0u);
+                }
+            };
+            using NS1 = IntTag<1>;
+            using NS2 = IntTag<2>;
 
             auto issue_scores = [&](int it) -> bool {
                 const int s = it % NSTAGE;
@@ -352,22 +366,24 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 if (it > 0 && !mbar_wait(bar_sc_empty, (it - 1) & 1)) { give_up(kStatusTimeoutMma); return false; }
                 tc_fence_after_sync();
                 if constexpr (MODE == kFwd) {
-                    score_mma(0, 0, 0, s, false);
+                    score_mma(NS1{}, 0, 0, 0, s, false);
                 } else if constexpr (MODE == kBwd1Row || MODE == kBwd1Col) {
-                    score_mma(0, 0, 0, s, false);     // S  = Q K^T      | S^T  = K Q^T
-                    score_mma(1, 1, 1, s, false);     // dP = dO V^T     | dP^T = V dO^T
+                    score_mma(NS1{}, 0, 0, 0, s, false);     // S  = Q K^T      | S^T  = K Q^T
+                    score_mma(NS1{}, 1, 1, 1, s, false);     // dP = dO V^T     | dP^T = V dO^T
                 } else if constexpr (MODE == kBwd2Row) {
-                    score_mma(0, 0, 0, s, false);                       // S  = Q K^T
-                    score_mma(1, 1, 1, s, false);                       // dP = dO V^T
-                    if (p.has_uq) score_mma(2, 2, 0, s, false);         // F  = uQ K^T
-                    if (p.has_uk) score_mma(2, 0, 2, s, p.has_uq);      //    + Q uK^T
-                    if (p.has_uv) score_mma(3, 1, 3, s, false);         // C  = dO uV^T
+                    // own: Q, dO, uQ;  swept: K, uK, V, uV;  accumulators: S, F, dP, C
+                    if (p.has_uk) score_mma(NS2{}, 0, 0, 0, s, false);      // S | F  = Q [K; uK]^T
+                    else          score_mma(NS1{}, 0, 0, 0, s, false);      // S      = Q K^T
+                    if (p.has_uq) score_mma(NS1{}, 1, 2, 0, s, p.has_uk);   // F     += uQ K^T
+                    if (p.has_uv) score_mma(NS2{}, 2, 1, 2, s, false);      // dP | C = dO [V; uV]^T
+                    else          score_mma(NS1{}, 2, 1, 2, s, false);      // dP     = dO V^T
                 } else {
-                    score_mma(0, 0, 0, s, false);                       // S^T  = K Q^T
-                    score_mma(1, 1, 1, s, false);                       // dP^T = V dO^T
-                    if (p.has_uq) score_mma(2, 0, 2, s, false);         // F^T  = K uQ^T
-                    if (p.has_uk) score_mma(2, 2, 0, s, p.has_uq);      //      + uK Q^T
-                    if (p.has_uv) score_mma(3, 3, 1, s, false);         // C^T  = uV dO^T
+                    // own: K, V, uK, uV;  swept: Q, uQ, dO;  accumulators: S^T, F^T, dP^T, C^T
+                    if (p.has_uq) score_mma(NS2{}, 0, 0, 0, s, false);      // S^T | F^T = K [Q; uQ]^T
+                    else          score_mma(NS1{}, 0, 0, 0, s, false);      // S^T       = K Q^T
+                    if (p.has_uk) score_mma(NS1{}, 1, 2, 0, s, p.has_uq);   // F^T      += uK Q^T
+                    score_mma(NS1{}, 2, 1, 2, s, false);                    // dP^T      = V dO^T
+                    if (p.has_uv) score_mma(NS1{}, 3, 3, 2, s, false);      // C^T       = uV dO^T
                 }
                 umma_commit(bar_sc_full);
                 return true;
@@ -395,15 +411,21 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         out_mma(0, 1, 0, s, acc);                       // dK += dS^T Q
                         out_mma(1, 0, 1, s, acc);                       // dV += P^T dO
                     } else if constexpr (MODE == kBwd2Row) {
-                        if (p.has_uv) out_mma(0, 0, 3, s, acc);         // dObar += P uV
-                        out_mma(0, 1, 1, s, acc || p.has_uv);           //        + (P*F) V
-                        out_mma(1, 2, 0, s, acc);                       // Omega += (P*T) K
-                        if (p.has_uk) out_mma(1, 3, 2, s, true);        //        + dS uK
-                        out_mma(2, 0, 0, s, acc);                       // PK    += P K
+                        // operands: P, P*F, P*T, dS;  outputs: PK, dObar, Omega
+                        if (KSUB == 1 && p.has_uv) {
+                            out_mma_pair(0, 0, 0, 3, s, acc);           // PK | dObar += P (K | uV)
+                        } else {
+                            out_mma(0, 0, 0, s, acc);                   // PK    += P K
+                            if (p.has_uv) out_mma(1, 0, 3, s, acc);     // dObar += P uV
+                        }
+                        out_mma(1, 1, 2, s, acc || p.has_uv);           // dObar += (P*F) V
+                        out_mma(2, 2, 0, s, acc);                       // Omega += (P*T) K
+                        if (p.has_uk) out_mma(2, 3, 1, s, true);        // Omega += dS uK
                     } else {
+                        // operands: Sbar^T, dS^T, (P*(F-alpha))^T;  outputs: Kbar, Vbar
                         out_mma(0, 0, 0, s, acc);                       // Kbar += Sbar^T Q
-                        if (p.has_uq) out_mma(0, 1, 2, s, true);        //       + dS^T uQ
-                        out_mma(1, 2, 1, s, acc);                       // Vbar += (P*(F-alpha))^T dO
+                        if (p.has_uq) out_mma(0, 1, 1, s, true);        // Kbar += dS^T uQ
+                        out_mma(1, 2, 2, s, acc);                       // Vbar += (P*(F-alpha))^T dO
                     }
                     umma_commit(bar_op_empty);
                     ++n_out;
@@ -416,11 +438,22 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         // =========================== pointwise threads =======================================
         const int row = tid & 127;               // own row inside the tile == tensor-memory lane
         const int sp = tid >> 7;                 // which 16-column slice of every score tile
+        const int col0 = sp * 16;                // my first column inside a swept tile
         const int own_idx = own0 + row;
         const bool own_ok = own_idx < n_own;
         const uint32_t tlane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         const float c_exp = p.scale * kLog2e;
         const long long row_stat = ((long long)batch * p.Hq + head) * p.Nq + own_idx;   // row-owned only
+
+        // where my 16 columns of operand k go in the swizzled operand tiles (two 16-byte chunks)
+        uint32_t op_addr[MT::NOPER][2];
+        #pragma unroll
+        for (int k = 0; k < MT::NOPER; ++k) {
+            const uint32_t tile = sbase + CFG::OFF_OPER + (k / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES;
+            const uint32_t chunk = ((k % CFG::OPER_PER_TILE) * TN + col0) >> 3;
+            op_addr[k][0] = tile + sw128_offset(row, chunk);
+            op_addr[k][1] = tile + sw128_offset(row, chunk + 1);
+        }
 
         // Synchronise the pointwise threads through an mbarrier so that the wait is bounded.
         uint32_t pw_phase = 0;
@@ -441,10 +474,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         };
         bool ok = true;
 
-        // per-row state
-        float L2 = 0.f, dlt = 0.f;               // row-owned: own row's lse*log2e and delta
-        float acc_a = 0.f, acc_b = 0.f;          // row sums (alpha, ecirc) or (running max, running sum)
-        if constexpr (MODE == kFwd) { acc_a = -1e30f; acc_b = 0.f; }
+        // per-row state (row-owned modes): -lse*log2e and -delta of my row
+        float nL2 = 0.f, ndlt = 0.f;
+        float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);   // row sums alpha, ecirc
+        float run_max = -1e30f, run_sum = 0.f;                                 // forward statistics sweep
 
         if constexpr (MODE == kBwd1Row) {
             // delta = rowsum(dO * out), each slice sums its share of the head dim
@@ -467,25 +500,30 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             }
             red_buf[sp * 128 + row] = part;
             ok = pw_sync();
+            float dlt = 0.f;
             #pragma unroll
             for (int k = 0; k < NSPLIT; ++k) dlt += red_buf[k * 128 + row];
             ok = ok && pw_sync();
             if (sp == 0 && own_ok) p.delta[row_stat] = dlt;
-            if (own_ok) L2 = p.lse[row_stat] * kLog2e;
+            ndlt = -dlt;
+            if (own_ok) nL2 = -p.lse[row_stat] * kLog2e;
         }
         if constexpr (MODE == kBwd2Row) {
-            if (own_ok) { L2 = p.lse[row_stat] * kLog2e; dlt = p.delta[row_stat]; }
+            if (own_ok) { nL2 = -p.lse[row_stat] * kLog2e; ndlt = -p.delta[row_stat]; }
         }
 
         int n_op = 0;                            // operand rounds written so far
-        for (int it = 0; ok && it < total; ++it) {
+
+        // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
+        auto tile_body = [&](auto full_tag, int it) -> bool {
+            constexpr bool FULL = decltype(full_tag)::value;
             const int outer = it / T;
             const int tile = t_lo + it % T;
             const int oth0 = tile * TN;
-            const int col0 = sp * 16;            // my first column inside the tile
 
             if constexpr (COL) {
-                // per-query statistics of this tile -> shared memory (double buffered)
+                // per-query statistics of this tile, negated, -> shared memory (double buffered):
+                // [-lse*log2e | -delta | -alpha | -ecirc], TN floats each
                 float* sb = stat_buf + (it & 1) * 4 * TN;
                 if (tid < TN) {
                     const int i = oth0 + tid;
@@ -496,19 +534,19 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         d = p.delta[off];
                         if constexpr (MODE == kBwd2Col) { al = p.alpha[off]; ec = p.ecirc[off]; }
                     }
-                    sb[tid] = l2; sb[TN + tid] = d; sb[2 * TN + tid] = al; sb[3 * TN + tid] = ec;
+                    sb[tid] = -l2; sb[TN + tid] = -d; sb[2 * TN + tid] = -al; sb[3 * TN + tid] = -ec;
                 }
                 // Buffer (it & 1) was last read in iteration it - 2; every thread has since waited
                 // for the output products of iteration it - 2, which start only after all threads
                 // finished that iteration, so the overwrite above cannot race with a reader.
-                if (!pw_sync()) { ok = false; break; }
+                if (!pw_sync()) return false;
             }
             if constexpr (MODE == kFwd) {
                 if (outer == 1 && it == T) {
-                    // between the two passes: combine the slices' (max, sum) into the row's lse
-                    red_buf[sp * 128 + row] = acc_a;
-                    red_buf[(NSPLIT + sp) * 128 + row] = acc_b;
-                    if (!pw_sync()) { ok = false; break; }
+                    // between the two sweeps: combine the slices' (max, sum) into the row's lse
+                    red_buf[sp * 128 + row] = run_max;
+                    red_buf[(NSPLIT + sp) * 128 + row] = run_sum;
+                    if (!pw_sync()) return false;
                     float m = -1e30f;
                     #pragma unroll
                     for (int k = 0; k < NSPLIT; ++k) m = fmaxf(m, red_buf[k * 128 + row]);
@@ -516,34 +554,38 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     #pragma unroll
                     for (int k = 0; k < NSPLIT; ++k)
                         l += red_buf[(NSPLIT + k) * 128 + row] * fast_exp2(red_buf[k * 128 + row] - m);
-                    L2 = (l > 0.f) ? m + log2f(l) : INFINITY;
+                    const float L2 = (l > 0.f) ? m + log2f(l) : INFINITY;
+                    nL2 = -L2;
                     if (sp == 0 && own_ok) p.lse[row_stat] = (l > 0.f) ? L2 * kLn2 : -INFINITY;
                 }
             }
 
-            if (!pw_wait(bar_sc_full, it & 1)) { ok = false; break; }
+            if (!pw_wait(bar_sc_full, it & 1)) return false;
             tc_fence_after_sync();
 
-            // ---- mask bookkeeping for my 16 columns -------------------------------------------
-            // dist = query position - key position; unmasked iff 0 <= dist (< window) when causal
-            long long dist0;                     // dist at my first column
-            int dstep;                           // change of dist per column
-            if constexpr (!COL) { dist0 = (long long)own_idx + p.delta_off - (oth0 + col0); dstep = -1; }
-            else                { dist0 = (long long)(oth0 + col0) + p.delta_off - own_idx; dstep = +1; }
-            uint32_t vmask = 0;                  // bit c set = column c unmasked
-            {
-                const int n_left = n_oth - (oth0 + col0);          // columns of mine inside the tensor
-                #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const long long dd = dist0 + (long long)dstep * c;
-                    bool v = own_ok && c < n_left;
-                    if (p.is_causal) v = v && dd >= 0 && (p.window == 0 || dd < p.window);
-                    vmask |= (v ? 1u : 0u) << c;
+            // ---- which of my 16 columns are unmasked: bits [mlo, mhi] of vmask ----------------
+            // dist = query position - key position; unmasked iff in range and, when causal,
+            // 0 <= dist (< window)
+            uint32_t vmask = 0xFFFFu;
+            if constexpr (!FULL) {
+                int mlo = 0, mhi = min(15, n_oth - (oth0 + col0) - 1);
+                if (p.is_causal) {
+                    if constexpr (!COL) {
+                        const int d0 = own_idx + doff - (oth0 + col0);       // dist falls with the column
+                        mhi = min(mhi, d0);
+                        if (p.window > 0) mlo = max(mlo, d0 - p.window + 1);
+                    } else {
+                        const int d0 = (oth0 + col0) + doff - own_idx;       // dist grows with the column
+                        mlo = max(mlo, -d0);
+                        if (p.window > 0) mhi = min(mhi, p.window - 1 - d0);
+                    }
                 }
+                vmask = (own_ok && mhi >= mlo) ? ((0xFFFFu >> (15 - mhi)) & (0xFFFFu << mlo)) : 0u;
             }
 
             float s_[16];
-            tmem_ld16(tlane + 0 * TN + col0, s_);
+            if constexpr (MODE == kFwd) tmem_ld16(tlane + 0 * TN + col0, s_);
+            else                        tmem_ld8(tlane + 0 * TN + col0, s_);
 
             if constexpr (MODE == kFwd) {
                 tmem_wait_ld();
@@ -551,103 +593,167 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_sc_empty);
                 if (outer == 0) {
-                    float mx = acc_a;
+                    float mx = run_max;
                     #pragma unroll
                     for (int c = 0; c < 16; ++c) {
-                        s_[c] = ((vmask >> c) & 1u) ? s_[c] * c_exp : -1e30f;
+                        s_[c] = (FULL || ((vmask >> c) & 1u)) ? s_[c] * c_exp : -1e30f;
                         mx = fmaxf(mx, s_[c]);
                     }
-                    float sum = acc_b * fast_exp2(acc_a - mx);
+                    float sum = run_sum * fast_exp2(run_max - mx);
                     #pragma unroll
                     for (int c = 0; c < 16; ++c)
-                        sum += ((vmask >> c) & 1u) ? fast_exp2(s_[c] - mx) : 0.f;
-                    acc_a = mx; acc_b = sum;
-                    continue;
+                        sum += (FULL || ((vmask >> c) & 1u)) ? fast_exp2(s_[c] - mx) : 0.f;
+                    run_max = mx; run_sum = sum;
+                    return true;
                 }
-                float pv[16];
-                #pragma unroll
-                for (int c = 0; c < 16; ++c)
-                    pv[c] = ((vmask >> c) & 1u) ? fast_exp2(s_[c] * c_exp - L2) : 0.f;
-                if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) { ok = false; break; }
-                store_operand16<BF16>(sbase + CFG::OFF_OPER, row, col0, pv);
-            } else {
-                float dp_[16];
-                tmem_ld16(tlane + 1 * TN + col0, dp_);
-                float f_[16], cc_[16];
-                if constexpr (MODE == kBwd2Row || MODE == kBwd2Col) {
-                    if (p.has_uq || p.has_uk) tmem_ld16(tlane + 2 * TN + col0, f_);
-                    if (p.has_uv) tmem_ld16(tlane + 3 * TN + col0, cc_);
-                }
-                tmem_wait_ld();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_sc_empty);
-                if constexpr (MODE == kBwd2Row || MODE == kBwd2Col) {
-                    if (!(p.has_uq || p.has_uk)) {
-                        #pragma unroll
-                        for (int c = 0; c < 16; ++c) f_[c] = 0.f;
-                    }
-                    if (!p.has_uv) {
-                        #pragma unroll
-                        for (int c = 0; c < 16; ++c) cc_[c] = 0.f;
-                    }
-                }
-                const float* sb = stat_buf + (it & 1) * 4 * TN + col0;   // column-owned only
-
-                // derived operands, packed to 16 bits as soon as they are formed
-                uint32_t w0[8], w1[8], w2[8], w3[8];
+                uint32_t w0[8];
                 #pragma unroll
                 for (int c2 = 0; c2 < 8; ++c2) {
-                    float e0[2], e1[2], e2[2], e3[2];
-                    #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int c = 2 * c2 + h;
-                        const bool v = (vmask >> c) & 1u;
-                        const float l2 = COL ? sb[c] : L2;
-                        const float dl = COL ? sb[TN + c] : dlt;
-                        const float pr = v ? fast_exp2(fmaf(s_[c], c_exp, -l2)) : 0.f;
-                        const float dps = dp_[c] - dl;
-                        e0[h] = e1[h] = e2[h] = e3[h] = 0.f;
-                        if constexpr (MODE == kBwd1Row) {
-                            e0[h] = pr * dps;                                 // dS
-                        } else if constexpr (MODE == kBwd1Col) {
-                            e0[h] = pr;                                       // P^T
-                            e1[h] = pr * dps;                                 // dS^T
-                        } else if constexpr (MODE == kBwd2Row) {
-                            const float f = p.scale * f_[c];
-                            const float t = fmaf(f, dps, cc_[c]);
-                            const float pf = pr * f, pt = pr * t;
-                            acc_a += pf; acc_b += pt;
-                            e0[h] = pr; e1[h] = pf; e2[h] = pt; e3[h] = pr * dps;
-                        } else {
-                            const float al = sb[2 * TN + c], ec = sb[3 * TN + c];
-                            const float f = p.scale * f_[c];
-                            const float t = fmaf(f, dps, cc_[c]);
-                            e0[h] = pr * (t - al * dps - ec);                 // Sbar^T
-                            e1[h] = pr * dps;                                 // dS^T
-                            e2[h] = pr * (f - al);                            // (P*(F-alpha))^T
+                    float a = fast_exp2(fmaf(s_[2 * c2], c_exp, nL2));
+                    float b = fast_exp2(fmaf(s_[2 * c2 + 1], c_exp, nL2));
+                    if constexpr (!FULL) {
+                        a = ((vmask >> (2 * c2)) & 1u) ? a : 0.f;
+                        b = ((vmask >> (2 * c2 + 1)) & 1u) ? b : 0.f;
+                    }
+                    w0[c2] = pack2<BF16>(a, b);
+                }
+                if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) return false;
+                st_shared_v4(op_addr[0][0], w0[0], w0[1], w0[2], w0[3]);
+                st_shared_v4(op_addr[0][1], w0[4], w0[5], w0[6], w0[7]);
+            } else {
+                // accumulator order: S, dP (first backward) or S, F, dP, C (second backward).
+                // My 16 columns are taken in two halves of 8 to bound the live registers; the
+                // score accumulators are handed back as soon as the second half is loaded.
+                const float2 cexp2 = make_float2(c_exp, c_exp);
+                const float2 scale2 = make_float2(p.scale, p.scale);
+                const bool has_f = BWD2 && (p.has_uq || p.has_uk);
+                const bool has_c = BWD2 && p.has_uv;
+                uint32_t w0[8], w1[8], w2[8], w3[8];
+                #pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int cb = col0 + 8 * half;
+                    float dp_[8], f_[8], cc_[8];
+                    if (half == 1) tmem_ld8(tlane + 0 * TN + cb, s_);
+                    tmem_ld8(tlane + (BWD2 ? 2 : 1) * TN + cb, dp_);
+                    if constexpr (BWD2) {
+                        if (has_f) tmem_ld8(tlane + 1 * TN + cb, f_);
+                        if (has_c) tmem_ld8(tlane + 3 * TN + cb, cc_);
+                    }
+                    tmem_wait_ld();
+                    if (half == 1) {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_sc_empty);
+                    }
+                    if constexpr (BWD2) {
+                        if (!has_f) {
+                            #pragma unroll
+                            for (int c = 0; c < 8; ++c) f_[c] = 0.f;
+                        }
+                        if (!has_c) {
+                            #pragma unroll
+                            for (int c = 0; c < 8; ++c) cc_[c] = 0.f;
                         }
                     }
-                    w0[c2] = pack2<BF16>(e0[0], e0[1]);
-                    if constexpr (MT::NOPER > 1) w1[c2] = pack2<BF16>(e1[0], e1[1]);
-                    if constexpr (MT::NOPER > 2) w2[c2] = pack2<BF16>(e2[0], e2[1]);
-                    if constexpr (MT::NOPER > 3) w3[c2] = pack2<BF16>(e3[0], e3[1]);
+                    // negated statistics of these columns (column-owned modes), four columns per load
+                    const float4* sb4 = reinterpret_cast<const float4*>(stat_buf + (it & 1) * 4 * TN + cb);
+                    #pragma unroll
+                    for (int c4 = 0; c4 < 2; ++c4) {
+                        float4 q_l2, q_dl, q_al, q_ec;
+                        if constexpr (COL) {
+                            q_l2 = sb4[c4]; q_dl = sb4[TN / 4 + c4];
+                            if constexpr (MODE == kBwd2Col) { q_al = sb4[2 * (TN / 4) + c4]; q_ec = sb4[3 * (TN / 4) + c4]; }
+                        }
+                        #pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int c = 4 * c4 + 2 * h;          // columns c, c + 1 of this half
+                            const int wi = 4 * half + (c >> 1);    // packed word index among my 16 columns
+                            const int mc = 8 * half + c;           // bit index in vmask
+                            float2 nl2, ndl, nal, nec;
+                            if constexpr (COL) {
+                                nl2 = h ? make_float2(q_l2.z, q_l2.w) : make_float2(q_l2.x, q_l2.y);
+                                ndl = h ? make_float2(q_dl.z, q_dl.w) : make_float2(q_dl.x, q_dl.y);
+                                if constexpr (MODE == kBwd2Col) {
+                                    nal = h ? make_float2(q_al.z, q_al.w) : make_float2(q_al.x, q_al.y);
+                                    nec = h ? make_float2(q_ec.z, q_ec.w) : make_float2(q_ec.x, q_ec.y);
+                                }
+                            } else {
+                                nl2 = make_float2(nL2, nL2);
+                                ndl = make_float2(ndlt, ndlt);
+                            }
+                            const float2 x = __ffma2_rn(make_float2(s_[c], s_[c + 1]), cexp2, nl2);
+                            float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                            if constexpr (!FULL) {
+                                pr.x = ((vmask >> mc) & 1u) ? pr.x : 0.f;
+                                pr.y = ((vmask >> (mc + 1)) & 1u) ? pr.y : 0.f;
+                            }
+                            const float2 dps = __fadd2_rn(make_float2(dp_[c], dp_[c + 1]), ndl);
+                            if constexpr (MODE == kBwd1Row) {
+                                const float2 ds = __fmul2_rn(pr, dps);
+                                w0[wi] = pack2<BF16>(ds.x, ds.y);                         // dS
+                            } else if constexpr (MODE == kBwd1Col) {
+                                const float2 ds = __fmul2_rn(pr, dps);
+                                w0[wi] = pack2<BF16>(pr.x, pr.y);                         // P^T
+                                w1[wi] = pack2<BF16>(ds.x, ds.y);                         // dS^T
+                            } else if constexpr (MODE == kBwd2Row) {
+                                const float2 f = __fmul2_rn(make_float2(f_[c], f_[c + 1]), scale2);
+                                const float2 t = __ffma2_rn(f, dps, make_float2(cc_[c], cc_[c + 1]));
+                                const float2 pf = __fmul2_rn(pr, f);
+                                const float2 pt = __fmul2_rn(pr, t);
+                                const float2 ds = __fmul2_rn(pr, dps);
+                                acc_a = __fadd2_rn(acc_a, pf);
+                                acc_b = __fadd2_rn(acc_b, pt);
+                                w0[wi] = pack2<BF16>(pr.x, pr.y);                         // P
+                                w1[wi] = pack2<BF16>(pf.x, pf.y);                         // P*F
+                                w2[wi] = pack2<BF16>(pt.x, pt.y);                         // P*T
+                                w3[wi] = pack2<BF16>(ds.x, ds.y);                         // dS
+                            } else {
+                                const float2 f = __fmul2_rn(make_float2(f_[c], f_[c + 1]), scale2);
+                                const float2 t = __ffma2_rn(f, dps, make_float2(cc_[c], cc_[c + 1]));
+                                const float2 u = __fadd2_rn(__ffma2_rn(nal, dps, t), nec);   // T - alpha (dP - delta) - ecirc
+                                const float2 sbar = __fmul2_rn(pr, u);
+                                const float2 ds = __fmul2_rn(pr, dps);
+                                const float2 ph = __fmul2_rn(pr, __fadd2_rn(f, nal));
+                                w0[wi] = pack2<BF16>(sbar.x, sbar.y);                     // Sbar^T
+                                w1[wi] = pack2<BF16>(ds.x, ds.y);                         // dS^T
+                                w2[wi] = pack2<BF16>(ph.x, ph.y);                         // (P*(F-alpha))^T
+                            }
+                        }
+                    }
                 }
-                if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) { ok = false; break; }
-                auto oper_addr = [&](int k) {
-                    return sbase + CFG::OFF_OPER + (k / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES;
-                };
-                auto oper_col = [&](int k) { return (k % CFG::OPER_PER_TILE) * TN + col0; };
-                store_operand_words(oper_addr(0), row, oper_col(0), w0);
-                if constexpr (MT::NOPER > 1) store_operand_words(oper_addr(1), row, oper_col(1), w1);
-                if constexpr (MT::NOPER > 2) store_operand_words(oper_addr(2), row, oper_col(2), w2);
-                if constexpr (MT::NOPER > 3) store_operand_words(oper_addr(3), row, oper_col(3), w3);
+                if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) return false;
+                st_shared_v4(op_addr[0][0], w0[0], w0[1], w0[2], w0[3]);
+                st_shared_v4(op_addr[0][1], w0[4], w0[5], w0[6], w0[7]);
+                if constexpr (MT::NOPER > 1) {
+                    st_shared_v4(op_addr[1][0], w1[0], w1[1], w1[2], w1[3]);
+                    st_shared_v4(op_addr[1][1], w1[4], w1[5], w1[6], w1[7]);
+                }
+                if constexpr (MT::NOPER > 2) {
+                    st_shared_v4(op_addr[2][0], w2[0], w2[1], w2[2], w2[3]);
+                    st_shared_v4(op_addr[2][1], w2[4], w2[5], w2[6], w2[7]);
+                }
+                if constexpr (MT::NOPER > 3) {
+                    st_shared_v4(op_addr[3][0], w3[0], w3[1], w3[2], w3[3]);
+                    st_shared_v4(op_addr[3][1], w3[4], w3[5], w3[6], w3[7]);
+                }
             }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_op_full);
             ++n_op;
-            if (__any_sync(0xffffffffu, aborted())) { ok = false; break; }
+            return !__any_sync(0xffffffffu, aborted());
+        };
+
+        for (int it = 0; ok && it < total; ++it) {
+            // is the whole 128 x TN tile pair unmasked and inside both tensors?  (uniform per CTA)
+            const int oth0 = (t_lo + it % T) * TN;
+            bool full = (own0 + 127 < n_own) && (oth0 + TN <= n_oth);
+            if (p.is_causal) {
+                const int dmin = COL ? (oth0 + doff - (own0 + 127)) : (own0 + doff - (oth0 + TN - 1));
+                const int dmax = COL ? (oth0 + TN - 1 + doff - own0) : (own0 + 127 + doff - oth0);
+                full = full && dmin >= 0 && (p.window == 0 || dmax < p.window);
+            }
+            ok = full ? tile_body(BoolTag<true>{}, it) : tile_body(BoolTag<false>{}, it);
         }
 
         // ---- epilogue ------------------------------------------------------------------------
@@ -657,8 +763,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         float alpha = 0.f, ecirc = 0.f;
         ok = __all_sync(0xffffffffu, ok);
         if constexpr (MODE == kBwd2Row) {
-            red_buf[sp * 128 + row] = acc_a;
-            red_buf[(NSPLIT + sp) * 128 + row] = acc_b;
+            red_buf[sp * 128 + row] = acc_a.x + acc_a.y;
+            red_buf[(NSPLIT + sp) * 128 + row] = acc_b.x + acc_b.y;
             if (ok) ok = pw_sync();
             #pragma unroll
             for (int k = 0; k < NSPLIT; ++k) { alpha += red_buf[k * 128 + row]; ecirc += red_buf[(NSPLIT + k) * 128 + row]; }
@@ -697,6 +803,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     store16_from_float<BF16>(p.res0, res_off + col, a0);
                     store16_from_float<BF16>(p.res1, res_off + col, a1);
                 } else {
+                    // accumulators: a0 = P K, a1 = P uV + (P*F) V, a2 = (P*T) K + dS uK
                     float o[16], g[16];
                     load16_as_float<BF16>(p.out, (long long)batch * p.out_sb + (long long)head * p.out_sh +
                                                      (long long)own_idx * p.out_sn + col, o);
@@ -704,8 +811,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                                                     (long long)own_idx * p.dQ_sn + col, g);
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float dob = a0[i] - alpha * o[i];                                   // dObar
-                        const float qb = p.scale * (a1[i] - ecirc * a2[i]) - alpha * g[i];        // Qbar
+                        const float dob = a1[i] - alpha * o[i];                                   // dObar
+                        const float qb = p.scale * (a2[i] - ecirc * a0[i]) - alpha * g[i];        // Qbar
                         a0[i] = qb; a1[i] = dob;
                     }
                     store16_from_float<BF16>(p.res0, res_off + col, a0);

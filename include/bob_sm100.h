@@ -102,9 +102,11 @@ int bob_sm100_bwd2(const bob_sm100_geom* geom, const void* q, const void* k, con
                    const void* dQ, const void* uQ, const void* uK, const void* uV, void* Qbar,
                    void* Kbar, void* Vbar, void* dObar, void* workspace, void* stream);
 
-/* Known-answer check of the tensor-core plumbing: a [128,64] x b [64,64] (same 16-bit format),
- * out[0] = a b^T, out[1] = a b, out[2] = a b^T with a staged through thread-written swizzled
- * shared memory; out is fp32 [3,128,64]; status is one device int. */
+/* Known-answer check of the tensor-core plumbing: a [128,64] x b [64,64] (same 16-bit format).
+ * out is fp32 [7,128,64]: out[0] = a b^T; out[1] = a b; out[2] = a b^T with a staged through
+ * thread-written swizzled shared memory; out[3], out[4] = the two halves of one 128-wide product
+ * a [b; b]^T; out[5], out[6] = the two halves of one 128-wide product a [b | b].
+ * status is one device int. */
 int bob_sm100_selftest(const void* a, const void* b, int is_bf16, float* out, int* status,
                        void* stream);
 
