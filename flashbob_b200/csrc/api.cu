@@ -110,6 +110,26 @@ static int dispatch_dtype(const bob_sm100_geom* g, SweepParams& prm, const Tenso
                                       : dispatch<MODE, false>(g, prm, tensors, stream);
 }
 
+// Profiling aid: BOB_SM100_BWD2_KERNELS=row or =col launches only that kernel of the second
+// backward (the column-owned kernel then reads whatever alpha / ecirc the workspace holds).
+static int bwd2_kernel_mask() {
+    const char* e = std::getenv("BOB_SM100_BWD2_KERNELS");
+    if (!e) return 3;
+    if (!std::strcmp(e, "row")) return 1;
+    if (!std::strcmp(e, "col")) return 2;
+    return 3;
+}
+
+// Builds with BOB_PHASE_TIMERS read a device pointer (hex) from BOB_SM100_PHASE_PTR: 16 counters.
+static long long* phase_pointer() {
+#ifdef BOB_PHASE_TIMERS
+    const char* e = std::getenv("BOB_SM100_PHASE_PTR");
+    return e ? reinterpret_cast<long long*>(std::strtoull(e, nullptr, 16)) : nullptr;
+#else
+    return nullptr;
+#endif
+}
+
 static void fill_common(const bob_sm100_geom* g, SweepParams& p, void* workspace) {
     std::memset(&p, 0, sizeof(p));
     p.B = g->B; p.Hq = g->Hq; p.Hkv = g->Hkv; p.G = g->Hq / g->Hkv; p.Nq = g->Nq; p.Nk = g->Nk;
@@ -122,16 +142,7 @@ static void fill_common(const bob_sm100_geom* g, SweepParams& p, void* workspace
     p.delta_off = static_cast<int>(d > (1 << 30) ? (1 << 30) : (d < -(1 << 30) ? -(1 << 30) : d));
     p.scale = g->scale;
     p.status = static_cast<int*>(workspace);
-}
-
-// Profiling aid: BOB_SM100_BWD2_KERNELS=row or =col launches only that kernel of the second
-// backward (the column-owned kernel then reads whatever alpha / ecirc the workspace holds).
-static int bwd2_kernel_mask() {
-    const char* e = std::getenv("BOB_SM100_BWD2_KERNELS");
-    if (!e) return 3;
-    if (!std::strcmp(e, "row")) return 1;
-    if (!std::strcmp(e, "col")) return 2;
-    return 3;
+    p.phase_cycles = phase_pointer();
 }
 
 static void set_strided(const void*& dst, long long& sb, long long& sh, long long& sn,

@@ -6,6 +6,8 @@
 //   out[3], out[4] = A * [B; B]^T  one N=128 K-major product over two adjacent B tiles
 //   out[5], out[6] = A * [B | B]   one N=128 MN-major product whose second 64 columns come from a
 //                                  tile `leading byte offset` away (merged output products)
+//   out[7] = A''* B^T  A'' written to tensor memory by threads and read from there (derived
+//                      operands that never touch shared memory)
 // A is [128, 64], B is [64, 64], both fp16 or both bf16 (kind::f16 needs one format for A and B).
 #include "ptx.cuh"
 #include "tmap.h"
@@ -28,7 +30,8 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
     const uint32_t tile_a2 = tile_b2 + 8192;      // 128 rows x 128 B
     const uint32_t bar_load = tile_a2 + 16384;
     const uint32_t bar_mma = bar_load + 8;
-    const uint32_t tmem_slot = bar_load + 16;
+    const uint32_t bar_mma2 = bar_load + 16;
+    const uint32_t tmem_slot = bar_load + 24;
     uint32_t* tmem_slot_ptr =
         reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
@@ -37,6 +40,7 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
     if (tid == 0) {
         mbar_init(bar_load, 1);
         mbar_init(bar_mma, 1);
+        mbar_init(bar_mma2, 1);
         mbar_fence_init();
     }
     if (warp == 0) {
@@ -63,6 +67,19 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
             st_shared_v4(tile_a2 + sw128_offset(tid, c), v.x, v.y, v.z, v.w);
         }
         fence_proxy_async_smem();
+    }
+    // ... and into tensor memory columns 448..479: row = lane, two elements per 32-bit column.
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(a_raw + tid * 64);
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16) + 448;
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint4 v0 = src[2 * c], v1 = src[2 * c + 1];
+            const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            tmem_st8(lane_base + 8 * c, w);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
     }
     bool ok = mbar_wait(bar_load, 0);
     __syncthreads();
@@ -111,6 +128,32 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
                 #pragma unroll
                 for (int i = 0; i < 16; ++i) out[(t * 128 + tid) * 64 + c + i] = v[i];
             }
+        }
+    } else {
+        atomicExch(status, 1);
+    }
+    // second round: the product with the tensor-memory operand reuses accumulator columns 0..63
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && ok) {
+        tc_fence_after_sync();
+        const uint32_t id_k = umma_idesc(fmt, fmt, 64, false);
+        #pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            umma_ts_lo(tmem + 0, tmem + 448 + ks * 8, ((tile_b + ks * 32) >> 4) | 0x10000u, id_k, ks > 0);
+        }
+        umma_commit(bar_mma2);
+    }
+    ok = ok && mbar_wait(bar_mma2, 0);
+    tc_fence_after_sync();
+    if (ok) {
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        for (int c = 0; c < 64; c += 16) {
+            float v[16];
+            tmem_ld16(lane_base + c, v);
+            tmem_wait_ld();
+            #pragma unroll
+            for (int i = 0; i < 16; ++i) out[(7 * 128 + tid) * 64 + c + i] = v[i];
         }
     } else {
         atomicExch(status, 1);

@@ -27,6 +27,18 @@
 
 namespace bob {
 
+// Optional in-kernel phase timers: with -DBOB_PHASE_TIMERS one pointwise thread and the MMA issuer of
+// every CTA add the SM cycles they spend in each phase to SweepParams::phase_cycles[0..15].
+#ifdef BOB_PHASE_TIMERS
+#define BOB_PH_DECL long long ph_t = clock64(); long long ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define BOB_PH(i) { const long long ph_n = clock64(); ph_acc[i] += ph_n - ph_t; ph_t = ph_n; }
+#define BOB_PH_FLUSH(base, on) if ((on) && p.phase_cycles) { for (int ph_i = 0; ph_i < 8; ++ph_i) atomicAdd(reinterpret_cast<unsigned long long*>(p.phase_cycles) + (base) + ph_i, (unsigned long long)ph_acc[ph_i]); }
+#else
+#define BOB_PH_DECL
+#define BOB_PH(i)
+#define BOB_PH_FLUSH(base, on)
+#endif
+
 enum Mode : int { kFwd = 0, kBwd1Row = 1, kBwd1Col = 2, kBwd2Row = 3, kBwd2Col = 4 };
 enum TensorId : int { kTQ = 0, kTK, kTV, kTDO, kTUQ, kTUK, kTUV, kNumTensors };
 
@@ -55,6 +67,7 @@ struct SweepParams {
     void* res1;
     void* res2;
     int* status;
+    long long* phase_cycles;      // optional cycle counters per pipeline phase (builds with BOB_PHASE_TIMERS)
 };
 
 template <int MODE> struct ModeTraits;
@@ -85,7 +98,6 @@ struct SweepConfig {
     static constexpr int NSPLIT = TN / 16;                 // 16 score columns per pointwise thread
     static constexpr int NPW = 128 * NSPLIT;               // pointwise threads
     static constexpr int NTHREADS = NPW + 64;              // + MMA warp + TMA warp
-    static constexpr int NSTAGE = 2;
     static constexpr int KSUB = DPAD / 64;                 // 64-element sub-tiles along the head dim
     static constexpr int OWN_TILE_BYTES = 128 * 128 * KSUB;
     static constexpr int OTH_SUB_BYTES = TN * 128;         // one 64-element-wide sub-tile of a swept tensor
@@ -98,14 +110,18 @@ struct SweepConfig {
     static constexpr int TMEM_NEED = SC_COLS + OUT_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
     static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
+    // three stages of swept tiles when shared memory allows (the TMA latency of a tile is then
+    // hidden behind two tiles of work), else two
+    static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + NOPER_TILES * OPER_TILE_BYTES + 16 * 1024;
+    static constexpr int NSTAGE = (FIXED_BYTES + 3 * OTH_STAGE_BYTES <= 232448) ? 3 : 2;
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int OFF_OWN = 0;
     static constexpr int OFF_OTH = OFF_OWN + MT::NOWN * OWN_TILE_BYTES;
     static constexpr int OFF_OPER = OFF_OTH + NSTAGE * OTH_STAGE_BYTES;
-    static constexpr int OFF_STAT = OFF_OPER + NOPER_TILES * OPER_TILE_BYTES;   // [2][4][TN] floats
-    static constexpr int OFF_RED = OFF_STAT + 2 * 4 * TN * 4;                   // [4][NSPLIT][128] floats
+    static constexpr int OFF_STAT = OFF_OPER + NOPER_TILES * OPER_TILE_BYTES;   // [NSTAGE][4][TN] floats
+    static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [4][NSPLIT][128] floats
     static constexpr int OFF_BAR = OFF_RED + 4 * NSPLIT * 128 * 4;
-    static constexpr int NBARS = 1 + 2 * NSTAGE + 6;
+    static constexpr int NBARS = 1 + 3 * NSTAGE + 6;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag
     static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;                     // + alignment slack
     static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
@@ -178,6 +194,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     const uint32_t bar_op_empty = bar_sc_full + 24;
     const uint32_t bar_done = bar_sc_full + 32;
     const uint32_t bar_pw = bar_sc_full + 40;
+    auto bar_stat = [&](int s) { return bar_sc_full + 48u + 8u * s; };    // per-stage: row statistics staged
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -223,7 +240,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     // ---- set-up ------------------------------------------------------------------------------
     if (tid == 0) {
         mbar_init(bar_own, 1);
-        for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); mbar_init(bar_stat(s), 32); }
         mbar_init(bar_sc_full, 1);
         mbar_init(bar_sc_empty, NPW / 32);
         mbar_init(bar_op_full, NPW / 32);
@@ -259,6 +276,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
 
     if (warp == NPW / 32 + 1) {
         // =========================== TMA producer =============================================
+        // Lane 0 issues the TMA copies.  In column-owned modes all 32 lanes also stage the swept
+        // tile's per-query statistics, negated, into the stage's statistics buffer:
+        // [-lse*log2e | -delta | -alpha | -ecirc], TN floats each.
         if (lane == 0) {
             uint32_t own_bytes = 0;
             #pragma unroll
@@ -274,16 +294,18 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     tma_load_4d(sbase + CFG::OFF_OWN + i * CFG::OWN_TILE_BYTES + ks * (128 * 128),
                                 &p.map[t], bar_own, ks * 64, own0, head, batch);
             }
-            int issued = 0;
-            for (int it = 0; it < total; ++it) {
-                const int s = it % NSTAGE;
-                if (it >= NSTAGE) {
-                    if (!mbar_wait(bar_empty(s), ((it / NSTAGE) - 1) & 1)) { give_up(kStatusTimeoutLoad); break; }
-                }
-                if (aborted()) break;
-                const int outer = it / T;
-                const int tile = t_lo + it % T;
-                const int oth_head = COL ? (head * p.G + outer) : kv_head;
+        }
+        int issued = 0;
+        for (int it = 0; it < total; ++it) {
+            const int s = it % NSTAGE;
+            bool go = true;
+            if (it >= NSTAGE) go = mbar_wait(bar_empty(s), ((it / NSTAGE) - 1) & 1);
+            go = __all_sync(0xffffffffu, go);
+            if (!go) { if (lane == 0) give_up(kStatusTimeoutLoad); break; }
+            const int outer = it / T;
+            const int tile = t_lo + it % T;
+            const int oth_head = COL ? (head * p.G + outer) : kv_head;
+            if (lane == 0) {
                 uint32_t bytes = 0;
                 #pragma unroll
                 for (int i = 0; i < MT::NOTH; ++i) {
@@ -300,9 +322,27 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     for (int ks = 0; ks < KSUB; ++ks)
                         tma_load_4d(oth_addr(s, ks, i), &p.map[t], bar_full(s), ks * 64, tile * TN, oth_head, batch);
                 }
-                ++issued;
             }
-            // Do not leave while copies into this CTA's shared memory may still be in flight.
+            if constexpr (COL) {
+                float* sb = stat_buf + s * 4 * TN;
+                #pragma unroll
+                for (int r = lane; r < TN; r += 32) {
+                    const int i = tile * TN + r;
+                    float l2 = 0.f, d = 0.f, al = 0.f, ec = 0.f;
+                    if (i < p.Nq) {
+                        const long long off = ((long long)batch * p.Hq + oth_head) * p.Nq + i;
+                        l2 = p.lse[off] * kLog2e;
+                        d = p.delta[off];
+                        if constexpr (MODE == kBwd2Col) { al = p.alpha[off]; ec = p.ecirc[off]; }
+                    }
+                    sb[r] = -l2; sb[TN + r] = -d; sb[2 * TN + r] = -al; sb[3 * TN + r] = -ec;
+                }
+                mbar_arrive(bar_stat(s));
+            }
+            ++issued;
+        }
+        // Do not leave while copies into this CTA's shared memory may still be in flight.
+        if (lane == 0) {
             for (int k = max(0, issued - NSTAGE); k < issued; ++k)
                 mbar_wait(bar_full(k % NSTAGE), (k / NSTAGE) & 1);
             mbar_wait(bar_own, 0);
@@ -311,59 +351,71 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         // =========================== MMA issuer ===============================================
         if (lane == 0 && total > 0) {
             constexpr uint32_t fmt = BF16 ? kFmtBF16 : kFmtF16;
-            const uint32_t own_base = sbase + CFG::OFF_OWN;
+
+            // Descriptor low words: (shared-memory address >> 4) | 0x10000 (leading byte offset 16).
+            // Everything but the pipeline stage is a compile-time offset from these three bases.
+            const uint32_t own16 = ((sbase + CFG::OFF_OWN) >> 4) | 0x10000u;
+            const uint32_t oper16 = ((sbase + CFG::OFF_OPER) >> 4) | 0x10000u;
+            const uint32_t oth16 = ((sbase + CFG::OFF_OTH) >> 4) | 0x10000u;
 
             // score-shaped product: acc[128, NS*TN] (+)= own[slot_a] * other[slot_b .. slot_b+NS-1]^T.
             // NS = 2 takes two adjacent swept tiles as one 2*TN-row operand and fills two adjacent
             // accumulators with one instruction per K step (the own tile is read once, not twice).
-            auto score_mma = [&](auto ns_tag, int acc, int slot_a, int slot_b, int stage, bool accumulate) {
+            auto score_mma = [&](auto ns_tag, int acc, int slot_a, int slot_b, uint32_t stage16, bool accumulate) {
                 constexpr int NS = decltype(ns_tag)::value;
                 constexpr uint32_t idesc = umma_idesc(fmt, fmt, NS * TN, false);
-                const uint32_t a = own_base + slot_a * CFG::OWN_TILE_BYTES;
+                const uint32_t a = own16 + ((slot_a * CFG::OWN_TILE_BYTES) >> 4);
+                const uint32_t b = stage16 + ((slot_b * CFG::OTH_SUB_BYTES) >> 4);
                 #pragma unroll
                 for (int ks = 0; ks < DPAD / 16; ++ks) {
-                    const uint32_t ao = (ks / 4) * (128 * 128) + (ks % 4) * 32;
-                    const uint32_t b = oth_addr(stage, ks / 4, slot_b) + (ks % 4) * 32;
-                    umma_ss(tmem + acc * TN, umma_smem_desc(a + ao), umma_smem_desc(b), idesc,
-                            (accumulate || ks > 0) ? 1u : 0u);
+                    const uint32_t ao = ((ks / 4) * (128 * 128) + (ks % 4) * 32) >> 4;
+                    const uint32_t bo = ((ks / 4) * (MT::NOTH * CFG::OTH_SUB_BYTES) + (ks % 4) * 32) >> 4;
+                    umma_ss_lo(tmem + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
                 }
             };
             // output-shaped product: out[128, DPAD] (+)= operand[oper] * other[slot_b]
-            auto out_mma = [&](int out, int oper, int slot_b, int stage, bool accumulate) {
+            auto out_mma = [&](int out, int oper, int slot_b, uint32_t stage16, bool accumulate) {
                 constexpr uint32_t idesc = umma_idesc(fmt, fmt, 64, true);
-                const uint32_t a = sbase + CFG::OFF_OPER + (oper / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES +
-                                   (oper % CFG::OPER_PER_TILE) * (TN * 2);
+                const uint32_t a = oper16 + (((oper / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES +
+                                              (oper % CFG::OPER_PER_TILE) * (TN * 2)) >> 4);
+                const uint32_t b = stage16 + ((slot_b * CFG::OTH_SUB_BYTES) >> 4);
                 #pragma unroll
                 for (int db = 0; db < KSUB; ++db) {
                     #pragma unroll
                     for (int ks = 0; ks < TN / 16; ++ks) {
-                        umma_ss(tmem_out + out * DPAD + db * 64, umma_smem_desc(a + ks * 32),
-                                umma_smem_desc(oth_addr(stage, db, slot_b) + ks * 2048), idesc,
-                                (accumulate || ks > 0) ? 1u : 0u);
+                        umma_ss_lo(tmem_out + out * DPAD + db * 64, a + ((ks * 32) >> 4),
+                                   b + ((db * MT::NOTH * CFG::OTH_SUB_BYTES + ks * 2048) >> 4), idesc,
+                                   (accumulate || ks > 0) ? 1u : 0u);
                     }
                 }
             };
             // two output-shaped products sharing the operand: (out, out+1)[128, 2*64] (+)=
             // operand[oper] * (other[slot_b] | other[slot_b2]); head dim <= 64 only
-            auto out_mma_pair = [&](int out, int oper, int slot_b, int slot_b2, int stage, bool accumulate) {
+            auto out_mma_pair = [&](int out, int oper, int slot_b, int slot_b2, uint32_t stage16, bool accumulate) {
                 constexpr uint32_t idesc = umma_idesc(fmt, fmt, 128, true);
-                const uint32_t a = sbase + CFG::OFF_OPER + (oper / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES +
-                                   (oper % CFG::OPER_PER_TILE) * (TN * 2);
-                const uint32_t lbo = (slot_b2 - slot_b) * CFG::OTH_SUB_BYTES;
+                const uint32_t a = oper16 + (((oper / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES +
+                                              (oper % CFG::OPER_PER_TILE) * (TN * 2)) >> 4);
+                // leading byte offset = distance between the two swept tiles (replaces the default 16)
+                const uint32_t lbo16 = ((slot_b2 - slot_b) * CFG::OTH_SUB_BYTES) >> 4;
+                const uint32_t b = (stage16 - 0x10000u) + ((slot_b * CFG::OTH_SUB_BYTES) >> 4) + (lbo16 << 16);
                 #pragma unroll
                 for (int ks = 0; ks < TN / 16; ++ks) {
-                    umma_ss(tmem_out + out * DPAD, umma_smem_desc(a + ks * 32),
-                            umma_smem_desc(oth_addr(stage, 0, slot_b) + ks * 2048, lbo), idesc,
-                            (accumulate || ks > 0) ? 1u : 0u);
+                    umma_ss_lo(tmem_out + out * DPAD, a + ((ks * 32) >> 4), b + ((ks * 2048) >> 4), idesc,
+                               (accumulate || ks > 0) ? 1u : 0u);
                 }
             };
             using NS1 = IntTag<1>;
             using NS2 = IntTag<2>;
 
+            BOB_PH_DECL
             auto issue_scores = [&](int it) -> bool {
-                const int s = it % NSTAGE;
-                if (!mbar_wait(bar_full(s), (it / NSTAGE) & 1)) { give_up(kStatusTimeoutMma); return false; }
+                const int stage = it % NSTAGE;
+                const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
+                BOB_PH(7)
+                if (!mbar_wait(bar_full(stage), (it / NSTAGE) & 1)) { give_up(kStatusTimeoutMma); return false; }
+                BOB_PH(0)
                 if (it > 0 && !mbar_wait(bar_sc_empty, (it - 1) & 1)) { give_up(kStatusTimeoutMma); return false; }
+                BOB_PH(1)
                 tc_fence_after_sync();
                 if constexpr (MODE == kFwd) {
                     score_mma(NS1{}, 0, 0, 0, s, false);
@@ -386,6 +438,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     if (p.has_uv) score_mma(NS1{}, 3, 3, 2, s, false);      // C^T       = uV dO^T
                 }
                 umma_commit(bar_sc_full);
+                BOB_PH(2)
                 return true;
             };
 
@@ -394,13 +447,15 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             ok = ok && issue_scores(0);
             int n_out = 0;      // output rounds issued so far
             for (int it = 0; ok && it < total; ++it) {
-                if (aborted()) break;
                 if (it + 1 < total && !issue_scores(it + 1)) break;
-                const int s = it % NSTAGE;
+                const int stage = it % NSTAGE;
+                const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
                 const int outer = it / T;
                 const bool has_out = (MODE != kFwd) || outer == 1;
                 if (has_out) {
+                    BOB_PH(7)
                     if (!mbar_wait(bar_op_full, n_out & 1)) { give_up(kStatusTimeoutMma); break; }
+                    BOB_PH(3)
                     tc_fence_after_sync();
                     const bool acc = n_out > 0;
                     if constexpr (MODE == kFwd) {
@@ -430,9 +485,11 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     umma_commit(bar_op_empty);
                     ++n_out;
                 }
-                umma_commit(bar_empty(s));
+                umma_commit(bar_empty(stage));
+                BOB_PH(4)
             }
             umma_commit(bar_done);
+            BOB_PH_FLUSH(8, true)
         }
     } else {
         // =========================== pointwise threads =======================================
@@ -513,6 +570,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
 
         int n_op = 0;                            // operand rounds written so far
+        BOB_PH_DECL
 
         // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
         auto tile_body = [&](auto full_tag, int it) -> bool {
@@ -521,26 +579,6 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             const int tile = t_lo + it % T;
             const int oth0 = tile * TN;
 
-            if constexpr (COL) {
-                // per-query statistics of this tile, negated, -> shared memory (double buffered):
-                // [-lse*log2e | -delta | -alpha | -ecirc], TN floats each
-                float* sb = stat_buf + (it & 1) * 4 * TN;
-                if (tid < TN) {
-                    const int i = oth0 + tid;
-                    float l2 = 0.f, d = 0.f, al = 0.f, ec = 0.f;
-                    if (i < p.Nq) {
-                        const long long off = ((long long)batch * p.Hq + (head * p.G + outer)) * p.Nq + i;
-                        l2 = p.lse[off] * kLog2e;
-                        d = p.delta[off];
-                        if constexpr (MODE == kBwd2Col) { al = p.alpha[off]; ec = p.ecirc[off]; }
-                    }
-                    sb[tid] = -l2; sb[TN + tid] = -d; sb[2 * TN + tid] = -al; sb[3 * TN + tid] = -ec;
-                }
-                // Buffer (it & 1) was last read in iteration it - 2; every thread has since waited
-                // for the output products of iteration it - 2, which start only after all threads
-                // finished that iteration, so the overwrite above cannot race with a reader.
-                if (!pw_sync()) return false;
-            }
             if constexpr (MODE == kFwd) {
                 if (outer == 1 && it == T) {
                     // between the two sweeps: combine the slices' (max, sum) into the row's lse
@@ -560,7 +598,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 }
             }
 
+            BOB_PH(7)
+            if constexpr (COL) {
+                // the swept tile's row statistics were staged by the producer warp
+                if (!pw_wait(bar_stat(it % NSTAGE), (it / NSTAGE) & 1)) return false;
+            }
             if (!pw_wait(bar_sc_full, it & 1)) return false;
+            BOB_PH(0)
             tc_fence_after_sync();
 
             // ---- which of my 16 columns are unmasked: bits [mlo, mhi] of vmask ----------------
@@ -640,6 +684,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         if (has_c) tmem_ld8(tlane + 3 * TN + cb, cc_);
                     }
                     tmem_wait_ld();
+                    BOB_PH(1)
                     if (half == 1) {
                         tc_fence_before_sync();
                         __syncwarp();
@@ -656,7 +701,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         }
                     }
                     // negated statistics of these columns (column-owned modes), four columns per load
-                    const float4* sb4 = reinterpret_cast<const float4*>(stat_buf + (it & 1) * 4 * TN + cb);
+                    const float4* sb4 = reinterpret_cast<const float4*>(stat_buf + (it % NSTAGE) * 4 * TN + cb);
                     #pragma unroll
                     for (int c4 = 0; c4 < 2; ++c4) {
                         float4 q_l2, q_dl, q_al, q_ec;
@@ -721,7 +766,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         }
                     }
                 }
+                BOB_PH(2)
                 if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) return false;
+                BOB_PH(3)
                 st_shared_v4(op_addr[0][0], w0[0], w0[1], w0[2], w0[3]);
                 st_shared_v4(op_addr[0][1], w0[4], w0[5], w0[6], w0[7]);
                 if constexpr (MT::NOPER > 1) {
@@ -741,7 +788,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_op_full);
             ++n_op;
-            return !__any_sync(0xffffffffu, aborted());
+            BOB_PH(4)
+            return true;
         };
 
         for (int it = 0; ok && it < total; ++it) {
@@ -756,6 +804,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             ok = full ? tile_body(BoolTag<true>{}, it) : tile_body(BoolTag<false>{}, it);
         }
 
+        BOB_PH_FLUSH(0, tid == 0)
         // ---- epilogue ------------------------------------------------------------------------
         if constexpr (MODE == kFwd) {
             if (total == 0 && sp == 0 && own_ok) p.lse[row_stat] = -INFINITY;

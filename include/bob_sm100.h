@@ -103,10 +103,10 @@ int bob_sm100_bwd2(const bob_sm100_geom* geom, const void* q, const void* k, con
                    void* Kbar, void* Vbar, void* dObar, void* workspace, void* stream);
 
 /* Known-answer check of the tensor-core plumbing: a [128,64] x b [64,64] (same 16-bit format).
- * out is fp32 [7,128,64]: out[0] = a b^T; out[1] = a b; out[2] = a b^T with a staged through
+ * out is fp32 [8,128,64]: out[0] = a b^T; out[1] = a b; out[2] = a b^T with a staged through
  * thread-written swizzled shared memory; out[3], out[4] = the two halves of one 128-wide product
- * a [b; b]^T; out[5], out[6] = the two halves of one 128-wide product a [b | b].
- * status is one device int. */
+ * a [b; b]^T; out[5], out[6] = the two halves of one 128-wide product a [b | b]; out[7] = a b^T
+ * with a written to and read from tensor memory.  status is one device int. */
 int bob_sm100_selftest(const void* a, const void* b, int is_bf16, float* out, int* status,
                        void* stream);
 

@@ -62,7 +62,7 @@ def test_tensor_core_plumbing_known_answer():
         g = torch.Generator().manual_seed(0)
         a = torch.randn(128, 64, generator=g).to(dtype).cuda()
         b = torch.randn(64, 64, generator=g).to(dtype).cuda()
-        out = torch.zeros(7, 128, 64, device="cuda")
+        out = torch.zeros(8, 128, 64, device="cuda")
         st = torch.zeros(1, dtype=torch.int32, device="cuda")
         rc = lib.bob_sm100_selftest(a.data_ptr(), b.data_ptr(), int(dtype == BF16), out.data_ptr(),
                                     st.data_ptr(), torch.cuda.current_stream().cuda_stream)
@@ -72,7 +72,7 @@ def test_tensor_core_plumbing_known_answer():
         torch.testing.assert_close(out[0].double(), ab_t, rtol=1e-5, atol=1e-4)
         torch.testing.assert_close(out[1].double(), ab, rtol=1e-5, atol=1e-4)
         torch.testing.assert_close(out[2].double(), ab_t, rtol=1e-5, atol=1e-4)
-        for i in (3, 4):
+        for i in (3, 4, 7):
             torch.testing.assert_close(out[i].double(), ab_t, rtol=1e-5, atol=1e-4)
         for i in (5, 6):
             torch.testing.assert_close(out[i].double(), ab, rtol=1e-5, atol=1e-4)
