@@ -226,8 +226,8 @@ def main():
     d = {n: t.to(dev) for n, t in host.items()}
     geom = dict(is_causal=True, window_size=0, q_offset=0, k_offset=0, scale=None)
     out, lse = ops.attention_forward(d["q"], d["k"], d["v"], **geom)
-    dQ, dK, dV, delta = ops.attention_first_backward(d["q"], d["k"], d["v"], out, lse, d["dO"], **geom)
-    d.update(out=out, lse=lse, dQ=dQ, delta=delta)
+    dQ, dK, dV, delta, pk = ops.attention_first_backward(d["q"], d["k"], d["v"], out, lse, d["dO"], **geom)
+    d.update(out=out, lse=lse, dQ=dQ, delta=delta, pk=pk)
     torch.cuda.synchronize()
 
     # ---- direct C-ABI call with preallocated results -------------------------------------------
@@ -244,7 +244,7 @@ def main():
 
     def bwd2(src):
         rc = lib.bob_sm100_bwd2(ctypes.byref(g), vp(src["q"]), vp(src["k"]), vp(src["v"]), vp(src["out"]),
-                                vp(src["lse"]), vp(src["delta"]), vp(src["dO"]), vp(src["dQ"]), vp(src["uQ"]),
+                                vp(src["lse"]), vp(src["delta"]), vp(src["pk"]), vp(src["dO"]), vp(src["dQ"]), vp(src["uQ"]),
                                 vp(src["uK"]), vp(src["uV"]), vp(res["Qbar"]), vp(res["Kbar"]), vp(res["Vbar"]),
                                 vp(res["dObar"]), vp(ws), ctypes.c_void_p(stream.cuda_stream))
         _lib.check(rc, "bob_sm100_bwd2")
@@ -300,7 +300,7 @@ def main():
     os.environ.pop("BOB_SM100_BWD2_KERNELS", None)
 
     # ---- end to end: pinned host buffers -> device -> C-ABI call -> pinned host results --------
-    names_in = ("q", "k", "v", "out", "lse", "delta", "dO", "dQ", "uQ", "uK", "uV")
+    names_in = ("q", "k", "v", "out", "lse", "delta", "pk", "dO", "dQ", "uQ", "uK", "uV")
     pin = {n: d[n].cpu().pin_memory() for n in names_in}
     stage = {n: torch.empty_like(d[n]) for n in names_in}
     pin_out = {n: torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for n, t in res.items()}

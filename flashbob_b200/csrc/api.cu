@@ -221,7 +221,7 @@ extern "C" int bob_sm100_fwd(const bob_sm100_geom* g, const void* q, const void*
 
 extern "C" int bob_sm100_bwd1(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
                               const void* out, const float* lse, const void* dO, void* dQ, void* dK,
-                              void* dV, float* delta, void* workspace, void* stream) {
+                              void* dV, float* delta, float* pk, void* workspace, void* stream) {
     int rc = check_geom(g);
     if (rc) return rc;
     if (!q || !k || !v || !out || !lse || !dO || !dQ || !dK || !dV || !delta) return kErrNull;
@@ -243,6 +243,7 @@ extern "C" int bob_sm100_bwd1(const bob_sm100_geom* g, const void* q, const void
     fill_common(g, p, workspace);
     p.lse = const_cast<float*>(lse);
     p.delta = delta;
+    p.pk = pk;
     set_strided(p.out, p.out_sb, p.out_sh, p.out_sn, out, g->out_strides);
     set_strided(p.dO, p.dO_sb, p.dO_sh, p.dO_sn, dO, g->do_strides);
     p.res0 = dQ;
@@ -254,13 +255,13 @@ extern "C" int bob_sm100_bwd1(const bob_sm100_geom* g, const void* q, const void
 }
 
 extern "C" int bob_sm100_bwd2(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
-                              const void* out, const float* lse, const float* delta, const void* dO,
-                              const void* dQ, const void* uQ, const void* uK, const void* uV,
+                              const void* out, const float* lse, const float* delta, const float* pk,
+                              const void* dO, const void* dQ, const void* uQ, const void* uK, const void* uV,
                               void* Qbar, void* Kbar, void* Vbar, void* dObar, void* workspace,
                               void* stream) {
     int rc = check_geom(g);
     if (rc) return rc;
-    if (!q || !k || !v || !out || !lse || !delta || !dO || !dQ || !Qbar || !Kbar || !Vbar || !dObar)
+    if (!q || !k || !v || !out || !lse || !delta || !pk || !dO || !dQ || !Qbar || !Kbar || !Vbar || !dObar)
         return kErrNull;
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256) return kErrWorkspace;
     if ((rc = check_strides(g->out_strides, out))) return rc;
@@ -284,6 +285,7 @@ extern "C" int bob_sm100_bwd2(const bob_sm100_geom* g, const void* q, const void
     p.has_uq = uQ != nullptr; p.has_uk = uK != nullptr; p.has_uv = uV != nullptr;
     p.lse = const_cast<float*>(lse);
     p.delta = const_cast<float*>(delta);
+    p.pk = const_cast<float*>(pk);
     const size_t stat_bytes = round256(static_cast<size_t>(g->B) * g->Hq * g->Nq * sizeof(float));
     p.alpha = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBlock);
     p.ecirc = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBlock + stat_bytes);

@@ -60,6 +60,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
 }
 
+// True in exactly one lane of a fully converged warp.  Code guarded by it runs in one thread while
+// the surrounding control flow stays warp-uniform, which lets the compiler keep addresses and
+// descriptors in uniform registers (tcgen05.mma and tcgen05.commit take uniform operands).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ----------------------------------------------------------------------------------------
 // proxies and fences
 // ----------------------------------------------------------------------------------------

@@ -7,9 +7,10 @@
 //      memory (fp32),
 //   2. reads them back (one thread per own row and per 16-column slice), applies the mask and the
 //      softmax recomputation from the saved log-sum-exp, builds the derived 16-bit operands and
-//      writes them into 128-byte-swizzled shared memory,
-//   3. accumulates output-shaped products  operand[128, TN] x other[TN, D]  into tensor memory
-//      accumulators that live for the whole sweep.
+//      writes them back into tensor memory (tcgen05.st),
+//   3. accumulates output-shaped products  operand[128, TN] x other[TN, D]  (operand read from
+//      tensor memory, swept tile MN-major from shared memory) into tensor memory accumulators
+//      that live for the whole sweep.
 // Column-owned stages compute the transposed scores (own = K-side), so the thread that owns key j
 // holds column j of the score matrix and the operands come out already transposed; the per-query
 // statistics then vary along the tensor-memory columns and are staged in shared memory.
@@ -62,6 +63,9 @@ struct SweepParams {
     float* delta;
     float* alpha;
     float* ecirc;
+    // fp32 [B, Hq, Nq, D]: PK = P K, written by the first backward (may be null there: not needed
+    // unless a second backward follows), read by the second backward's row-owned kernel
+    float* pk;
     // results, contiguous [B, H, N, D] in the input dtype
     void* res0;
     void* res1;
@@ -72,9 +76,9 @@ struct SweepParams {
 
 template <int MODE> struct ModeTraits;
 template <> struct ModeTraits<kFwd>     { static constexpr int NOWN = 1, NOTH = 2, NSC = 1, NOUT = 1, NOPER = 1; static constexpr bool COL = false; };
-template <> struct ModeTraits<kBwd1Row> { static constexpr int NOWN = 2, NOTH = 2, NSC = 2, NOUT = 1, NOPER = 1; static constexpr bool COL = false; };
+template <> struct ModeTraits<kBwd1Row> { static constexpr int NOWN = 2, NOTH = 2, NSC = 2, NOUT = 2, NOPER = 2; static constexpr bool COL = false; };
 template <> struct ModeTraits<kBwd1Col> { static constexpr int NOWN = 2, NOTH = 2, NSC = 2, NOUT = 2, NOPER = 2; static constexpr bool COL = true; };
-template <> struct ModeTraits<kBwd2Row> { static constexpr int NOWN = 3, NOTH = 4, NSC = 4, NOUT = 3, NOPER = 4; static constexpr bool COL = false; };
+template <> struct ModeTraits<kBwd2Row> { static constexpr int NOWN = 3, NOTH = 4, NSC = 4, NOUT = 2, NOPER = 4; static constexpr bool COL = false; };
 template <> struct ModeTraits<kBwd2Col> { static constexpr int NOWN = 4, NOTH = 3, NSC = 4, NOUT = 2, NOPER = 3; static constexpr bool COL = true; };
 
 // Which global tensor fills own slot / other slot `i` of a mode.
@@ -102,23 +106,22 @@ struct SweepConfig {
     static constexpr int OWN_TILE_BYTES = 128 * 128 * KSUB;
     static constexpr int OTH_SUB_BYTES = TN * 128;         // one 64-element-wide sub-tile of a swept tensor
     static constexpr int OTH_STAGE_BYTES = KSUB * MT::NOTH * OTH_SUB_BYTES;   // laid out [sub][slot]
-    static constexpr int OPER_PER_TILE = 64 / TN;          // operands packed per 128-byte-row tile
-    static constexpr int NOPER_TILES = (MT::NOPER + OPER_PER_TILE - 1) / OPER_PER_TILE;
-    static constexpr int OPER_TILE_BYTES = 128 * 128;
+    // tensor memory map: [score accumulators | derived 16-bit operands | output accumulators]
     static constexpr int SC_COLS = MT::NSC * TN;
+    static constexpr int OPER_COLS_EACH = TN / 2;          // 128 x TN 16-bit values, two per 32-bit column
+    static constexpr int OPER_COLS = MT::NOPER * OPER_COLS_EACH;
     static constexpr int OUT_COLS = MT::NOUT * DPAD;
-    static constexpr int TMEM_NEED = SC_COLS + OUT_COLS;
+    static constexpr int TMEM_NEED = SC_COLS + OPER_COLS + OUT_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
     static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
     // three stages of swept tiles when shared memory allows (the TMA latency of a tile is then
     // hidden behind two tiles of work), else two
-    static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + NOPER_TILES * OPER_TILE_BYTES + 16 * 1024;
+    static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + 16 * 1024;
     static constexpr int NSTAGE = (FIXED_BYTES + 3 * OTH_STAGE_BYTES <= 232448) ? 3 : 2;
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int OFF_OWN = 0;
     static constexpr int OFF_OTH = OFF_OWN + MT::NOWN * OWN_TILE_BYTES;
-    static constexpr int OFF_OPER = OFF_OTH + NSTAGE * OTH_STAGE_BYTES;
-    static constexpr int OFF_STAT = OFF_OPER + NOPER_TILES * OPER_TILE_BYTES;   // [NSTAGE][4][TN] floats
+    static constexpr int OFF_STAT = OFF_OTH + NSTAGE * OTH_STAGE_BYTES;         // [NSTAGE][4][TN] floats
     static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [4][NSPLIT][128] floats
     static constexpr int OFF_BAR = OFF_RED + 4 * NSPLIT * 128 * 4;
     static constexpr int NBARS = 1 + 3 * NSTAGE + 6;
@@ -258,7 +261,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = misc[0];
-    const uint32_t tmem_out = tmem + CFG::SC_COLS;
+    const uint32_t tmem_oper = tmem + CFG::SC_COLS;
+    const uint32_t tmem_out = tmem_oper + CFG::OPER_COLS;
 
     auto give_up = [&](int code) {
         misc[1] = 1;
@@ -296,14 +300,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             }
         }
         int issued = 0;
+        int s = 0, round = 0;                    // pipeline stage of iteration `it`, and it / NSTAGE
+        int tile = t_lo, outer = 0;              // swept tile of iteration `it`, and it / T
         for (int it = 0; it < total; ++it) {
-            const int s = it % NSTAGE;
             bool go = true;
-            if (it >= NSTAGE) go = mbar_wait(bar_empty(s), ((it / NSTAGE) - 1) & 1);
+            if (it >= NSTAGE) go = mbar_wait(bar_empty(s), (round - 1) & 1);
             go = __all_sync(0xffffffffu, go);
             if (!go) { if (lane == 0) give_up(kStatusTimeoutLoad); break; }
-            const int outer = it / T;
-            const int tile = t_lo + it % T;
             const int oth_head = COL ? (head * p.G + outer) : kv_head;
             if (lane == 0) {
                 uint32_t bytes = 0;
@@ -340,6 +343,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 mbar_arrive(bar_stat(s));
             }
             ++issued;
+            if (++s == NSTAGE) { s = 0; ++round; }
+            if (++tile == t_hi) { tile = t_lo; ++outer; }
         }
         // Do not leave while copies into this CTA's shared memory may still be in flight.
         if (lane == 0) {
@@ -349,13 +354,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
     } else if (warp == NPW / 32) {
         // =========================== MMA issuer ===============================================
-        if (lane == 0 && total > 0) {
+        if (total > 0) {
             constexpr uint32_t fmt = BF16 ? kFmtBF16 : kFmtF16;
 
             // Descriptor low words: (shared-memory address >> 4) | 0x10000 (leading byte offset 16).
             // Everything but the pipeline stage is a compile-time offset from these three bases.
             const uint32_t own16 = ((sbase + CFG::OFF_OWN) >> 4) | 0x10000u;
-            const uint32_t oper16 = ((sbase + CFG::OFF_OPER) >> 4) | 0x10000u;
             const uint32_t oth16 = ((sbase + CFG::OFF_OTH) >> 4) | 0x10000u;
 
             // score-shaped product: acc[128, NS*TN] (+)= own[slot_a] * other[slot_b .. slot_b+NS-1]^T.
@@ -370,51 +374,38 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 for (int ks = 0; ks < DPAD / 16; ++ks) {
                     const uint32_t ao = ((ks / 4) * (128 * 128) + (ks % 4) * 32) >> 4;
                     const uint32_t bo = ((ks / 4) * (MT::NOTH * CFG::OTH_SUB_BYTES) + (ks % 4) * 32) >> 4;
-                    umma_ss_lo(tmem + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
+                    if (elect_one()) umma_ss_lo(tmem + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
                 }
             };
-            // output-shaped product: out[128, DPAD] (+)= operand[oper] * other[slot_b]
+            // output-shaped product: out[128, DPAD] (+)= operand[oper] * other[slot_b]; the operand is
+            // read from tensor memory (8 columns per 16-element K step), the swept tile MN-major
+            // from shared memory
             auto out_mma = [&](int out, int oper, int slot_b, uint32_t stage16, bool accumulate) {
                 constexpr uint32_t idesc = umma_idesc(fmt, fmt, 64, true);
-                const uint32_t a = oper16 + (((oper / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES +
-                                              (oper % CFG::OPER_PER_TILE) * (TN * 2)) >> 4);
+                const uint32_t a = tmem_oper + oper * CFG::OPER_COLS_EACH;
                 const uint32_t b = stage16 + ((slot_b * CFG::OTH_SUB_BYTES) >> 4);
                 #pragma unroll
                 for (int db = 0; db < KSUB; ++db) {
                     #pragma unroll
                     for (int ks = 0; ks < TN / 16; ++ks) {
-                        umma_ss_lo(tmem_out + out * DPAD + db * 64, a + ((ks * 32) >> 4),
-                                   b + ((db * MT::NOTH * CFG::OTH_SUB_BYTES + ks * 2048) >> 4), idesc,
-                                   (accumulate || ks > 0) ? 1u : 0u);
+                        if (elect_one())
+                            umma_ts_lo(tmem_out + out * DPAD + db * 64, a + ks * 8,
+                                       b + ((db * MT::NOTH * CFG::OTH_SUB_BYTES + ks * 2048) >> 4), idesc,
+                                       (accumulate || ks > 0) ? 1u : 0u);
                     }
-                }
-            };
-            // two output-shaped products sharing the operand: (out, out+1)[128, 2*64] (+)=
-            // operand[oper] * (other[slot_b] | other[slot_b2]); head dim <= 64 only
-            auto out_mma_pair = [&](int out, int oper, int slot_b, int slot_b2, uint32_t stage16, bool accumulate) {
-                constexpr uint32_t idesc = umma_idesc(fmt, fmt, 128, true);
-                const uint32_t a = oper16 + (((oper / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES +
-                                              (oper % CFG::OPER_PER_TILE) * (TN * 2)) >> 4);
-                // leading byte offset = distance between the two swept tiles (replaces the default 16)
-                const uint32_t lbo16 = ((slot_b2 - slot_b) * CFG::OTH_SUB_BYTES) >> 4;
-                const uint32_t b = (stage16 - 0x10000u) + ((slot_b * CFG::OTH_SUB_BYTES) >> 4) + (lbo16 << 16);
-                #pragma unroll
-                for (int ks = 0; ks < TN / 16; ++ks) {
-                    umma_ss_lo(tmem_out + out * DPAD, a + ((ks * 32) >> 4), b + ((ks * 2048) >> 4), idesc,
-                               (accumulate || ks > 0) ? 1u : 0u);
                 }
             };
             using NS1 = IntTag<1>;
             using NS2 = IntTag<2>;
 
             BOB_PH_DECL
-            auto issue_scores = [&](int it) -> bool {
-                const int stage = it % NSTAGE;
+            // scores of iteration `it`, whose swept tiles sit in pipeline stage `stage` (use number `round`)
+            auto issue_scores = [&](int it, int stage, int round) -> bool {
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
                 BOB_PH(7)
-                if (!mbar_wait(bar_full(stage), (it / NSTAGE) & 1)) { give_up(kStatusTimeoutMma); return false; }
+                if (!__all_sync(0xffffffffu, mbar_wait(bar_full(stage), round & 1))) { give_up(kStatusTimeoutMma); return false; }
                 BOB_PH(0)
-                if (it > 0 && !mbar_wait(bar_sc_empty, (it - 1) & 1)) { give_up(kStatusTimeoutMma); return false; }
+                if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_sc_empty, (it - 1) & 1))) { give_up(kStatusTimeoutMma); return false; }
                 BOB_PH(1)
                 tc_fence_after_sync();
                 if constexpr (MODE == kFwd) {
@@ -437,24 +428,24 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     score_mma(NS1{}, 2, 1, 2, s, false);                    // dP^T      = V dO^T
                     if (p.has_uv) score_mma(NS1{}, 3, 3, 2, s, false);      // C^T       = uV dO^T
                 }
-                umma_commit(bar_sc_full);
+                if (elect_one()) umma_commit(bar_sc_full);
                 BOB_PH(2)
                 return true;
             };
 
-            bool ok = mbar_wait(bar_own, 0);
+            bool ok = __all_sync(0xffffffffu, mbar_wait(bar_own, 0));
             if (!ok) give_up(kStatusTimeoutMma);
-            ok = ok && issue_scores(0);
+            ok = ok && issue_scores(0, 0, 0);
             int n_out = 0;      // output rounds issued so far
+            int stage = 0;                            // stage of iteration `it`
+            int nstage = (NSTAGE > 1) ? 1 : 0, nround = (NSTAGE > 1) ? 0 : 1;   // stage / use number of iteration it + 1
             for (int it = 0; ok && it < total; ++it) {
-                if (it + 1 < total && !issue_scores(it + 1)) break;
-                const int stage = it % NSTAGE;
+                if (it + 1 < total && !issue_scores(it + 1, nstage, nround)) break;
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
-                const int outer = it / T;
-                const bool has_out = (MODE != kFwd) || outer == 1;
+                const bool has_out = (MODE != kFwd) || it >= T;
                 if (has_out) {
                     BOB_PH(7)
-                    if (!mbar_wait(bar_op_full, n_out & 1)) { give_up(kStatusTimeoutMma); break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar_op_full, n_out & 1))) { give_up(kStatusTimeoutMma); break; }
                     BOB_PH(3)
                     tc_fence_after_sync();
                     const bool acc = n_out > 0;
@@ -462,34 +453,32 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         out_mma(0, 0, 1, s, acc);                       // O += P V
                     } else if constexpr (MODE == kBwd1Row) {
                         out_mma(0, 0, 0, s, acc);                       // dQ += dS K
+                        if (p.pk) out_mma(1, 1, 0, s, acc);             // PK += P K
                     } else if constexpr (MODE == kBwd1Col) {
                         out_mma(0, 1, 0, s, acc);                       // dK += dS^T Q
                         out_mma(1, 0, 1, s, acc);                       // dV += P^T dO
                     } else if constexpr (MODE == kBwd2Row) {
-                        // operands: P, P*F, P*T, dS;  outputs: PK, dObar, Omega
-                        if (KSUB == 1 && p.has_uv) {
-                            out_mma_pair(0, 0, 0, 3, s, acc);           // PK | dObar += P (K | uV)
-                        } else {
-                            out_mma(0, 0, 0, s, acc);                   // PK    += P K
-                            if (p.has_uv) out_mma(1, 0, 3, s, acc);     // dObar += P uV
-                        }
-                        out_mma(1, 1, 2, s, acc || p.has_uv);           // dObar += (P*F) V
-                        out_mma(2, 2, 0, s, acc);                       // Omega += (P*T) K
-                        if (p.has_uk) out_mma(2, 3, 1, s, true);        // Omega += dS uK
+                        // operands: P, P*F, P*T, dS;  swept: K, uK, V, uV;  outputs: dObar, Omega
+                        if (p.has_uv) out_mma(0, 0, 3, s, acc);         // dObar += P uV
+                        out_mma(0, 1, 2, s, acc || p.has_uv);           // dObar += (P*F) V
+                        out_mma(1, 2, 0, s, acc);                       // Omega += (P*T) K
+                        if (p.has_uk) out_mma(1, 3, 1, s, true);        // Omega += dS uK
                     } else {
                         // operands: Sbar^T, dS^T, (P*(F-alpha))^T;  outputs: Kbar, Vbar
                         out_mma(0, 0, 0, s, acc);                       // Kbar += Sbar^T Q
                         if (p.has_uq) out_mma(0, 1, 1, s, true);        // Kbar += dS^T uQ
                         out_mma(1, 2, 2, s, acc);                       // Vbar += (P*(F-alpha))^T dO
                     }
-                    umma_commit(bar_op_empty);
+                    if (elect_one()) umma_commit(bar_op_empty);
                     ++n_out;
                 }
-                umma_commit(bar_empty(stage));
+                if (elect_one()) umma_commit(bar_empty(stage));
+                stage = nstage;
+                if (++nstage == NSTAGE) { nstage = 0; ++nround; }
                 BOB_PH(4)
             }
-            umma_commit(bar_done);
-            BOB_PH_FLUSH(8, true)
+            if (elect_one()) umma_commit(bar_done);
+            BOB_PH_FLUSH(8, lane == 0)
         }
     } else {
         // =========================== pointwise threads =======================================
@@ -502,15 +491,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         const float c_exp = p.scale * kLog2e;
         const long long row_stat = ((long long)batch * p.Hq + head) * p.Nq + own_idx;   // row-owned only
 
-        // where my 16 columns of operand k go in the swizzled operand tiles (two 16-byte chunks)
-        uint32_t op_addr[MT::NOPER][2];
-        #pragma unroll
-        for (int k = 0; k < MT::NOPER; ++k) {
-            const uint32_t tile = sbase + CFG::OFF_OPER + (k / CFG::OPER_PER_TILE) * CFG::OPER_TILE_BYTES;
-            const uint32_t chunk = ((k % CFG::OPER_PER_TILE) * TN + col0) >> 3;
-            op_addr[k][0] = tile + sw128_offset(row, chunk);
-            op_addr[k][1] = tile + sw128_offset(row, chunk + 1);
-        }
+        // where my 16 columns (8 packed words) of operand k go in tensor memory
+        const uint32_t op_taddr = tlane + CFG::SC_COLS + (col0 >> 1);
 
         // Synchronise the pointwise threads through an mbarrier so that the wait is bounded.
         uint32_t pw_phase = 0;
@@ -573,10 +555,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         BOB_PH_DECL
 
         // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
-        auto tile_body = [&](auto full_tag, int it) -> bool {
+        auto tile_body = [&](auto full_tag, int it, int tile, int outer, int stage, int round) -> bool {
             constexpr bool FULL = decltype(full_tag)::value;
-            const int outer = it / T;
-            const int tile = t_lo + it % T;
             const int oth0 = tile * TN;
 
             if constexpr (MODE == kFwd) {
@@ -601,7 +581,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             BOB_PH(7)
             if constexpr (COL) {
                 // the swept tile's row statistics were staged by the producer warp
-                if (!pw_wait(bar_stat(it % NSTAGE), (it / NSTAGE) & 1)) return false;
+                if (!pw_wait(bar_stat(stage), round & 1)) return false;
             }
             if (!pw_wait(bar_sc_full, it & 1)) return false;
             BOB_PH(0)
@@ -662,8 +642,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     w0[c2] = pack2<BF16>(a, b);
                 }
                 if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) return false;
-                st_shared_v4(op_addr[0][0], w0[0], w0[1], w0[2], w0[3]);
-                st_shared_v4(op_addr[0][1], w0[4], w0[5], w0[6], w0[7]);
+                tmem_st8(op_taddr, w0);
             } else {
                 // accumulator order: S, dP (first backward) or S, F, dP, C (second backward).
                 // My 16 columns are taken in two halves of 8 to bound the live registers; the
@@ -701,7 +680,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         }
                     }
                     // negated statistics of these columns (column-owned modes), four columns per load
-                    const float4* sb4 = reinterpret_cast<const float4*>(stat_buf + (it % NSTAGE) * 4 * TN + cb);
+                    const float4* sb4 = reinterpret_cast<const float4*>(stat_buf + stage * 4 * TN + cb);
                     #pragma unroll
                     for (int c4 = 0; c4 < 2; ++c4) {
                         float4 q_l2, q_dl, q_al, q_ec;
@@ -736,6 +715,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                             if constexpr (MODE == kBwd1Row) {
                                 const float2 ds = __fmul2_rn(pr, dps);
                                 w0[wi] = pack2<BF16>(ds.x, ds.y);                         // dS
+                                w1[wi] = pack2<BF16>(pr.x, pr.y);                         // P
                             } else if constexpr (MODE == kBwd1Col) {
                                 const float2 ds = __fmul2_rn(pr, dps);
                                 w0[wi] = pack2<BF16>(pr.x, pr.y);                         // P^T
@@ -769,22 +749,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 BOB_PH(2)
                 if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) return false;
                 BOB_PH(3)
-                st_shared_v4(op_addr[0][0], w0[0], w0[1], w0[2], w0[3]);
-                st_shared_v4(op_addr[0][1], w0[4], w0[5], w0[6], w0[7]);
-                if constexpr (MT::NOPER > 1) {
-                    st_shared_v4(op_addr[1][0], w1[0], w1[1], w1[2], w1[3]);
-                    st_shared_v4(op_addr[1][1], w1[4], w1[5], w1[6], w1[7]);
-                }
-                if constexpr (MT::NOPER > 2) {
-                    st_shared_v4(op_addr[2][0], w2[0], w2[1], w2[2], w2[3]);
-                    st_shared_v4(op_addr[2][1], w2[4], w2[5], w2[6], w2[7]);
-                }
-                if constexpr (MT::NOPER > 3) {
-                    st_shared_v4(op_addr[3][0], w3[0], w3[1], w3[2], w3[3]);
-                    st_shared_v4(op_addr[3][1], w3[4], w3[5], w3[6], w3[7]);
-                }
+                tmem_st8(op_taddr + 0 * CFG::OPER_COLS_EACH, w0);
+                if constexpr (MT::NOPER > 1) tmem_st8(op_taddr + 1 * CFG::OPER_COLS_EACH, w1);
+                if constexpr (MT::NOPER > 2) tmem_st8(op_taddr + 2 * CFG::OPER_COLS_EACH, w2);
+                if constexpr (MT::NOPER > 3) tmem_st8(op_taddr + 3 * CFG::OPER_COLS_EACH, w3);
             }
-            fence_proxy_async_smem();
+            tmem_wait_st();
+            tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_op_full);
             ++n_op;
@@ -792,16 +763,20 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             return true;
         };
 
+        int tile = t_lo, outer = 0, stage = 0, round = 0;
         for (int it = 0; ok && it < total; ++it) {
             // is the whole 128 x TN tile pair unmasked and inside both tensors?  (uniform per CTA)
-            const int oth0 = (t_lo + it % T) * TN;
+            const int oth0 = tile * TN;
             bool full = (own0 + 127 < n_own) && (oth0 + TN <= n_oth);
             if (p.is_causal) {
                 const int dmin = COL ? (oth0 + doff - (own0 + 127)) : (own0 + doff - (oth0 + TN - 1));
                 const int dmax = COL ? (oth0 + TN - 1 + doff - own0) : (own0 + 127 + doff - oth0);
                 full = full && dmin >= 0 && (p.window == 0 || dmax < p.window);
             }
-            ok = full ? tile_body(BoolTag<true>{}, it) : tile_body(BoolTag<false>{}, it);
+            ok = full ? tile_body(BoolTag<true>{}, it, tile, outer, stage, round)
+                      : tile_body(BoolTag<false>{}, it, tile, outer, stage, round);
+            if (++tile == t_hi) { tile = t_lo; ++outer; }
+            if (++stage == NSTAGE) { stage = 0; ++round; }
         }
 
         BOB_PH_FLUSH(0, tid == 0)
@@ -829,15 +804,14 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             for (int c = 0; c < DC; c += 16) {
                 const int col = sp * DC + c;
                 if (col >= p.D) break;
-                float a0[16], a1[16], a2[16];
+                float a0[16], a1[16];
                 if (total > 0) {
-                    tmem_ld16(tlane + CFG::SC_COLS + 0 * DPAD + col, a0);
-                    if constexpr (MT::NOUT > 1) tmem_ld16(tlane + CFG::SC_COLS + 1 * DPAD + col, a1);
-                    if constexpr (MT::NOUT > 2) tmem_ld16(tlane + CFG::SC_COLS + 2 * DPAD + col, a2);
+                    tmem_ld16(tlane + CFG::SC_COLS + CFG::OPER_COLS + 0 * DPAD + col, a0);
+                    if constexpr (MT::NOUT > 1) tmem_ld16(tlane + CFG::SC_COLS + CFG::OPER_COLS + 1 * DPAD + col, a1);
                     tmem_wait_ld();
                 } else {
                     #pragma unroll
-                    for (int i = 0; i < 16; ++i) { a0[i] = 0.f; a1[i] = 0.f; a2[i] = 0.f; }
+                    for (int i = 0; i < 16; ++i) { a0[i] = 0.f; a1[i] = 0.f; }
                 }
                 if (!own_ok) continue;          // tensor-memory loads above are warp-wide; stores are per row
                 if constexpr (MODE == kFwd) {
@@ -845,23 +819,37 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 } else if constexpr (MODE == kBwd1Row) {
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) a0[i] *= p.scale;
-                    store16_from_float<BF16>(p.res0, res_off + col, a0);
+                    store16_from_float<BF16>(p.res0, res_off + col, a0);                          // dQ
+                    if (p.pk) {
+                        float4* dst = reinterpret_cast<float4*>(p.pk + res_off + col);            // PK
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            dst[i] = make_float4(a1[4 * i], a1[4 * i + 1], a1[4 * i + 2], a1[4 * i + 3]);
+                    }
                 } else if constexpr (MODE == kBwd1Col || MODE == kBwd2Col) {
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) a0[i] *= p.scale;
                     store16_from_float<BF16>(p.res0, res_off + col, a0);
                     store16_from_float<BF16>(p.res1, res_off + col, a1);
                 } else {
-                    // accumulators: a0 = P K, a1 = P uV + (P*F) V, a2 = (P*T) K + dS uK
-                    float o[16], g[16];
+                    // accumulators: a0 = P uV + (P*F) V, a1 = (P*T) K + dS uK;  PK comes from the first backward
+                    float o[16], g[16], pkv[16];
+                    {
+                        const float4* src = reinterpret_cast<const float4*>(p.pk + res_off + col);
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 t = src[i];
+                            pkv[4 * i] = t.x; pkv[4 * i + 1] = t.y; pkv[4 * i + 2] = t.z; pkv[4 * i + 3] = t.w;
+                        }
+                    }
                     load16_as_float<BF16>(p.out, (long long)batch * p.out_sb + (long long)head * p.out_sh +
                                                      (long long)own_idx * p.out_sn + col, o);
                     load16_as_float<BF16>(p.dQ, (long long)batch * p.dQ_sb + (long long)head * p.dQ_sh +
                                                     (long long)own_idx * p.dQ_sn + col, g);
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float dob = a1[i] - alpha * o[i];                                   // dObar
-                        const float qb = p.scale * (a2[i] - ecirc * a0[i]) - alpha * g[i];        // Qbar
+                        const float dob = a0[i] - alpha * o[i];                                   // dObar
+                        const float qb = p.scale * (a1[i] - ecirc * pkv[i]) - alpha * g[i];       // Qbar
                         a0[i] = qb; a1[i] = dob;
                     }
                     store16_from_float<BF16>(p.res0, res_off + col, a0);

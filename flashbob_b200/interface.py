@@ -170,18 +170,18 @@ class BoBSecondOrder(Function):
         ctx.set_materialize_grads(False)
         geom = dict(is_causal=is_causal, window_size=window_size, q_offset=q_offset,
                     k_offset=k_offset, scale=scale)
-        dQ, dK, dV, delta = ops.attention_first_backward(q, k, v, out, lse, dO, **geom)
-        ctx.save_for_backward(q, k, v, out, lse, dO, dQ, delta)
+        dQ, dK, dV, delta, pk = ops.attention_first_backward(q, k, v, out, lse, dO, **geom)
+        ctx.save_for_backward(q, k, v, out, lse, dO, dQ, delta, pk)
         ctx.geom = geom
         return dQ, dK, dV
 
     @staticmethod
     def backward(ctx, uQ, uK, uV):
-        q, k, v, out, lse, dO, dQ, delta = ctx.saved_tensors
+        q, k, v, out, lse, dO, dQ, delta, pk = ctx.saved_tensors
         if uQ is None and uK is None and uV is None:
             return (None,) * 11
         Qbar, Kbar, Vbar, dObar = ops.attention_second_backward(
-            q, k, v, out, lse, delta, dO, dQ, uQ, uK, uV, **ctx.geom)
+            q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, **ctx.geom)
         return (Qbar, Kbar, Vbar, dObar, None, None, None, None, None, None, None)
 
 
@@ -204,7 +204,8 @@ class SDPAWithBoB(Function):
         q, k, v, out, lse = ctx.saved_tensors
         g = ctx.geom
         if not torch.is_grad_enabled():
-            dQ, dK, dV, _ = ops.attention_first_backward(q, k, v, out, lse, dO, **g)
+            dQ, dK, dV, _, _ = ops.attention_first_backward(q, k, v, out, lse, dO,
+                                                            for_second_order=False, **g)
         else:
             dQ, dK, dV = BoBSecondOrder.apply(q, k, v, dO, out, lse, g["q_offset"], g["k_offset"],
                                               g["is_causal"], g["window_size"], g["scale"])

@@ -105,8 +105,9 @@ def attention_forward(q, k, v, *, is_causal, window_size, q_offset, k_offset, sc
 
 
 def attention_first_backward(q, k, v, out, lse, dO, *, is_causal, window_size, q_offset, k_offset,
-                             scale):
-    """dQ, dK, dV (input dtype, contiguous) and delta = rowsum(dO*out) [B,Hq,Nq] (fp32)."""
+                             scale, for_second_order=True):
+    """dQ, dK, dV (input dtype, contiguous), delta = rowsum(dO*out) [B,Hq,Nq] (fp32) and, when
+    `for_second_order`, pk = softmax(S) K [B,Hq,Nq,D] (fp32) for the second backward (else None)."""
     _require_cuda_16bit(q, k, v, out, dO)
     lib = _lib.load()
     q, k, v, out, dO = (_tma_ready(t) for t in (q, k, v, out, dO))
@@ -119,24 +120,25 @@ def attention_first_backward(q, k, v, out, lse, dO, *, is_causal, window_size, q
     dK = torch.empty(k.shape, dtype=q.dtype, device=q.device)
     dV = torch.empty(k.shape, dtype=q.dtype, device=q.device)
     delta = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+    pk = torch.empty(q.shape, dtype=torch.float32, device=q.device) if for_second_order else None
     ws = _workspace(_lib.STAGE_BWD1, g, q.device)
     with torch.cuda.device(q.device):
         rc = lib.bob_sm100_bwd1(ctypes.byref(g), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse),
-                                _ptr(dO), _ptr(dQ), _ptr(dK), _ptr(dV), _ptr(delta), _ptr(ws),
+                                _ptr(dO), _ptr(dQ), _ptr(dK), _ptr(dV), _ptr(delta), _ptr(pk), _ptr(ws),
                                 _stream(q.device))
     _lib.check(rc, "bob_sm100_bwd1")
     _finish(ws, q.device, "bob_sm100_bwd1")
-    return dQ, dK, dV, delta
+    return dQ, dK, dV, delta, pk
 
 
-def attention_second_backward(q, k, v, out, lse, delta, dO, dQ, uQ, uK, uV, *, is_causal,
+def attention_second_backward(q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, *, is_causal,
                               window_size, q_offset, k_offset, scale):
     """Qbar, Kbar, Vbar, dObar (input dtype, contiguous).  uQ/uK/uV may be None."""
     _require_cuda_16bit(q, k, v, out, dO, dQ, uQ, uK, uV)
     lib = _lib.load()
     q, k, v, out, dO, dQ = (_tma_ready(t) for t in (q, k, v, out, dO, dQ))
     uQ, uK, uV = (None if t is None else _tma_ready(t.to(q.dtype)) for t in (uQ, uK, uV))
-    lse, delta = lse.contiguous(), delta.contiguous()
+    lse, delta, pk = lse.contiguous(), delta.contiguous(), pk.contiguous()
     g = _geom(q, k, is_causal=is_causal, window_size=window_size, q_offset=q_offset,
               k_offset=k_offset, scale=scale)
     for field, t in ((g.q_strides, q), (g.k_strides, k), (g.v_strides, v), (g.out_strides, out),
@@ -151,7 +153,7 @@ def attention_second_backward(q, k, v, out, lse, delta, dO, dQ, uQ, uK, uV, *, i
     ws = _workspace(_lib.STAGE_BWD2, g, q.device)
     with torch.cuda.device(q.device):
         rc = lib.bob_sm100_bwd2(ctypes.byref(g), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse),
-                                _ptr(delta), _ptr(dO), _ptr(dQ), _ptr(uQ), _ptr(uK), _ptr(uV),
+                                _ptr(delta), _ptr(pk), _ptr(dO), _ptr(dQ), _ptr(uQ), _ptr(uK), _ptr(uV),
                                 _ptr(Qbar), _ptr(Kbar), _ptr(Vbar), _ptr(dObar), _ptr(ws),
                                 _stream(q.device))
     _lib.check(rc, "bob_sm100_bwd2")

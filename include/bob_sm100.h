@@ -89,18 +89,20 @@ int bob_sm100_read_status(const void* workspace, void* stream);
 int bob_sm100_fwd(const bob_sm100_geom* geom, const void* q, const void* k, const void* v,
                   void* out, float* lse, void* workspace, void* stream);
 
-/* First backward: dQ, dK, dV for cotangent dO, and delta = rowsum(dO * out). */
+/* First backward: dQ, dK, dV for cotangent dO, and delta = rowsum(dO * out).
+ * pk (nullable): fp32 [B, Hq, Nq, D], receives softmax(S) K, a by-product the second backward
+ * needs; pass NULL when no second backward will follow (plain first-order training). */
 int bob_sm100_bwd1(const bob_sm100_geom* geom, const void* q, const void* k, const void* v,
                    const void* out, const float* lse, const void* dO, void* dQ, void* dK,
-                   void* dV, float* delta, void* workspace, void* stream);
+                   void* dV, float* delta, float* pk, void* workspace, void* stream);
 
 /* Second backward: gradients of <uQ, dQ> + <uK, dK> + <uV, dV> with respect to q, k, v and dO.
  * uQ / uK / uV may be NULL: that tangent is undefined and contributes nothing.
- * dQ is the first-backward result for the same inputs (bob_sm100_bwd1's output). */
+ * dQ, delta and pk are the first-backward results for the same inputs (bob_sm100_bwd1's outputs). */
 int bob_sm100_bwd2(const bob_sm100_geom* geom, const void* q, const void* k, const void* v,
-                   const void* out, const float* lse, const float* delta, const void* dO,
-                   const void* dQ, const void* uQ, const void* uK, const void* uV, void* Qbar,
-                   void* Kbar, void* Vbar, void* dObar, void* workspace, void* stream);
+                   const void* out, const float* lse, const float* delta, const float* pk,
+                   const void* dO, const void* dQ, const void* uQ, const void* uK, const void* uV,
+                   void* Qbar, void* Kbar, void* Vbar, void* dObar, void* workspace, void* stream);
 
 /* Known-answer check of the tensor-core plumbing: a [128,64] x b [64,64] (same 16-bit format).
  * out is fp32 [8,128,64]: out[0] = a b^T; out[1] = a b; out[2] = a b^T with a staged through

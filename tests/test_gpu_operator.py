@@ -159,8 +159,8 @@ def test_second_backward_is_linear_in_the_tangents_at_full_size():
     c = lambda t: t.cuda()
     qd, kd, vd, dOd = map(c, (q, k, v, dO))
     out, lse = ops.attention_forward(qd, kd, vd, **geom)
-    dQ, dK, dV, delta = ops.attention_first_backward(qd, kd, vd, out, lse, dOd, **geom)
-    run = lambda a, b, cc: ops.attention_second_backward(qd, kd, vd, out, lse, delta, dOd, dQ, a, b, cc, **geom)
+    dQ, dK, dV, delta, pk = ops.attention_first_backward(qd, kd, vd, out, lse, dOd, **geom)
+    run = lambda a, b, cc: ops.attention_second_backward(qd, kd, vd, out, lse, delta, pk, dOd, dQ, a, b, cc, **geom)
     full = run(c(u1), c(k1), c(v1))
     parts_q = run(c(u1), None, None)
     parts_kv = run(None, c(k1), c(v1))

@@ -43,8 +43,8 @@ def _run_kernels(q, k, v, dO, uQ, uK, uV, geom):
     c = lambda t: None if t is None else t.cuda()
     qd, kd, vd, dOd, uQd, uKd, uVd = map(c, (q, k, v, dO, uQ, uK, uV))
     out, lse = ops.attention_forward(qd, kd, vd, **geom)
-    dQ, dK, dV, delta = ops.attention_first_backward(qd, kd, vd, out, lse, dOd, **geom)
-    Qb, Kb, Vb, dOb = ops.attention_second_backward(qd, kd, vd, out, lse, delta, dOd, dQ, uQd, uKd,
+    dQ, dK, dV, delta, pk = ops.attention_first_backward(qd, kd, vd, out, lse, dOd, **geom)
+    Qb, Kb, Vb, dOb = ops.attention_second_backward(qd, kd, vd, out, lse, delta, pk, dOd, dQ, uQd, uKd,
                                                     uVd, **geom)
     return dict(out=out, dQ=dQ, dK=dK, dV=dV, Qbar=Qb, Kbar=Kb, Vbar=Vb, dObar=dOb), lse, delta
 
@@ -169,8 +169,8 @@ def test_strided_inputs_are_read_in_place():
     qd, kd, vd, dOd, uQd, uKd, uVd = map(tr, (q, k, v, dO, uQ, uK, uV))
     assert not qd.is_contiguous() and ops._tma_ready(qd) is qd
     out, lse = ops.attention_forward(qd, kd, vd, **geom)
-    dQ, dK, dV, delta = ops.attention_first_backward(qd, kd, vd, out, lse, dOd, **geom)
-    res = ops.attention_second_backward(qd, kd, vd, out, lse, delta, dOd, dQ, uQd, uKd, uVd, **geom)
+    dQ, dK, dV, delta, pk = ops.attention_first_backward(qd, kd, vd, out, lse, dOd, **geom)
+    res = ops.attention_second_backward(qd, kd, vd, out, lse, delta, pk, dOd, dQ, uQd, uKd, uVd, **geom)
     for n, t in zip(O.OUTPUT_NAMES, (out, dQ, dK, dV, *res)):
         _check(f"strided:{n}", t, getattr(ref, n), BF16)
     # a layout the kernels cannot address (odd row stride) is copied, not rejected
