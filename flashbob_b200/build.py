@@ -17,7 +17,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libbob_sm100.so"
-SOURCES = ("api.cu", "selftest.cu")
+SOURCES = ("api.cu", "selftest.cu", "noalloc.cu")
 HEADERS = ("ptx.cuh", "sweep.cuh", "tmap.h")
 
 

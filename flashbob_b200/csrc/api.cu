@@ -170,6 +170,8 @@ extern "C" const char* bob_sm100_error_string(int code) {
         case kErrAttr: return "cannot raise the dynamic shared memory limit";
         case kErrAlign: return "tensor base address must be 16-byte aligned";
         case kErrNoDriver: return "cuTensorMapEncodeTiled is unavailable in this driver";
+        case -11: return "cannot resolve the built-in scratch array on this device";
+        case -12: return "problem too large for the built-in scratch (B*Hq*Nq > 1048576 rows)";
         case -101: return "tensor base address must be 16-byte aligned";
         case -102: return "tensor strides unusable for TMA";
         case kStatusTimeoutLoad: return "device: a wait for a TMA load ran out";

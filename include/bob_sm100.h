@@ -104,6 +104,23 @@ int bob_sm100_bwd2(const bob_sm100_geom* geom, const void* q, const void* k, con
                    const void* dO, const void* dQ, const void* uQ, const void* uK, const void* uV,
                    void* Qbar, void* Kbar, void* Vbar, void* dObar, void* workspace, void* stream);
 
+/* Second backward without a caller-provided workspace (no counterpart in the reference).
+ * For hosts that cannot allocate or hand over scratch memory at call time - a plug-in inside a
+ * runtime that owns all device memory, a loop that forbids allocator calls after start-up.  The
+ * scratch is a fixed array inside the library: 8 MiB + 256 B of device memory on every GPU that
+ * loads the library, held until process exit.  Limit: B * Hq * Nq <= bob_sm100_noalloc_max_rows()
+ * (1,048,576); beyond it the call returns -12 and enqueues nothing.  The first call on a device
+ * resolves the array's device address (make that call before any stream capture begins).  All calls
+ * share the array, which keeps the last call's contents; calls whose kernels overlap on the GPU
+ * race on it, so issue them on one stream or otherwise serialise them.  Arguments and results are
+ * those of bob_sm100_bwd2 without `workspace`; no device memory is allocated or freed. */
+size_t bob_sm100_noalloc_max_rows(void);
+int bob_sm100_bwd2_noalloc(const bob_sm100_geom* geom, const void* q, const void* k, const void* v,
+                           const void* out, const float* lse, const float* delta, const float* pk,
+                           const void* dO, const void* dQ, const void* uQ, const void* uK,
+                           const void* uV, void* Qbar, void* Kbar, void* Vbar, void* dObar,
+                           void* stream);
+
 /* Known-answer check of the tensor-core plumbing: a [128,64] x b [64,64] (same 16-bit format).
  * out is fp32 [8,128,64]: out[0] = a b^T; out[1] = a b; out[2] = a b^T with a staged through
  * thread-written swizzled shared memory; out[3], out[4] = the two halves of one 128-wide product
