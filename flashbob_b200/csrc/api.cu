@@ -57,10 +57,10 @@ struct TensorArg {
     bool q_side;              // [B, Hq, Nq, D] (true) or [B, Hkv, Nk, D] (false)
 };
 
-template <int MODE, int DPAD, int TN, bool BF16>
+template <int MODE, int DPAD, int TN, bool BF16, int NG = 1, int CW = 16>
 static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
                         cudaStream_t stream) {
-    using CFG = SweepConfig<MODE, DPAD, TN>;
+    using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
     using MT = ModeTraits<MODE>;
     auto build = [&](int t, int box_rows) -> int {
         const TensorArg& a = tensors[t];
@@ -79,7 +79,7 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
         int rc = build(other_tensor<MODE>(i), TN);
         if (rc) return rc;
     }
-    auto kernel = sweep_kernel<MODE, DPAD, TN, BF16>;
+    auto kernel = sweep_kernel<MODE, DPAD, TN, BF16, NG, CW>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CFG::SMEM_BYTES) !=
         cudaSuccess)
         return kErrAttr;
@@ -91,16 +91,20 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
     return cudaGetLastError() == cudaSuccess ? 0 : kErrLaunch;
 }
 
-// Tile width of the swept side per stage and head dimension: the widest that fits tensor memory
-// (512 columns) and shared memory (227 KB).
+// Tile table.  Head dim <= 64: 64-wide swept tiles everywhere; the second backward gives each
+// pointwise thread 32 columns (256 threads with room to prefetch tensor-memory loads).  Head dim
+// 128: 64-wide tiles except the second backward, whose four score accumulators and three or four
+// operands leave tensor memory (512 columns) room for 32-wide tiles only.
 template <int MODE, bool BF16>
 static int dispatch(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
                     cudaStream_t stream) {
-    if (g->D <= 64) return launch_sweep<MODE, 64, 64, BF16>(g, prm, tensors, stream);
-    if constexpr (MODE == kBwd2Row || MODE == kBwd2Col)
-        return launch_sweep<MODE, 128, 32, BF16>(g, prm, tensors, stream);
-    else
-        return launch_sweep<MODE, 128, 64, BF16>(g, prm, tensors, stream);
+    constexpr bool kSecond = (MODE == kBwd2Row || MODE == kBwd2Col);
+    if (g->D <= 64) {
+        if constexpr (kSecond) return launch_sweep<MODE, 64, 64, BF16, 1, 32>(g, prm, tensors, stream);
+        else                   return launch_sweep<MODE, 64, 64, BF16>(g, prm, tensors, stream);
+    }
+    if constexpr (kSecond) return launch_sweep<MODE, 128, 32, BF16>(g, prm, tensors, stream);
+    else                   return launch_sweep<MODE, 128, 64, BF16>(g, prm, tensors, stream);
 }
 
 template <int MODE>

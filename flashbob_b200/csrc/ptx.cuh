@@ -1,4 +1,4 @@
-// Thin inline-PTX layer for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, no multicast),
+// Thin inline-PTX layer for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, each CTA loads its own tiles),
 // tensor memory (tcgen05.alloc/ld/st) and the 5th-generation tensor-core MMA (tcgen05.mma).
 //
 // Every wait in this file is bounded: a wait that does not complete within kWaitCycleLimit

@@ -96,11 +96,18 @@ template <int MODE> __host__ __device__ constexpr int other_tensor(int i) {
     return i == 0 ? kTQ : (i == 1 ? kTUQ : kTDO);                                          // Q, uQ adjacent
 }
 
-template <int MODE, int DPAD, int TN>
+template <int MODE, int DPAD, int TN, int NG = 1, int CW = 16>
 struct SweepConfig {
     using MT = ModeTraits<MODE>;
-    static constexpr int NSPLIT = TN / 16;                 // 16 score columns per pointwise thread
-    static constexpr int NPW = 128 * NSPLIT;               // pointwise threads
+    // NG pointwise groups take the swept tiles in turn (group g: tiles g, g + NG, ...), each with its
+    // own score accumulators and operand columns, so that one group's tensor-memory latencies hide
+    // behind the other group's arithmetic and the MMA warp always has a tile to work on.
+    // CW score columns per pointwise thread: 16 (more threads, 96 registers each) or 32 (half the
+    // threads with 168 registers each, enough to keep the next tensor-memory loads in flight while
+    // the current columns are computed)
+    static constexpr int NSPLIT = TN / CW;
+    static constexpr int GP = 128 * NSPLIT;                // pointwise threads per group
+    static constexpr int NPW = GP * NG;                    // pointwise threads
     static constexpr int NTHREADS = NPW + 64;              // + MMA warp + TMA warp
     static constexpr int KSUB = DPAD / 64;                 // 64-element sub-tiles along the head dim
     static constexpr int OWN_TILE_BYTES = 128 * 128 * KSUB;
@@ -111,20 +118,22 @@ struct SweepConfig {
     static constexpr int OPER_COLS_EACH = TN / 2;          // 128 x TN 16-bit values, two per 32-bit column
     static constexpr int OPER_COLS = MT::NOPER * OPER_COLS_EACH;
     static constexpr int OUT_COLS = MT::NOUT * DPAD;
-    static constexpr int TMEM_NEED = SC_COLS + OPER_COLS + OUT_COLS;
+    static constexpr int TMEM_NEED = NG * (SC_COLS + OPER_COLS) + OUT_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
     static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
-    // three stages of swept tiles when shared memory allows (the TMA latency of a tile is then
-    // hidden behind two tiles of work), else two
+    // as many stages of swept tiles as shared memory allows, between 2 and 3 (5 with two groups,
+    // whose tiles are half as wide): the TMA latency of a tile hides behind the tiles before it
     static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + 16 * 1024;
-    static constexpr int NSTAGE = (FIXED_BYTES + 3 * OTH_STAGE_BYTES <= 232448) ? 3 : 2;
+    static constexpr int STAGE_ROOM = (232448 - FIXED_BYTES) / OTH_STAGE_BYTES;
+    static constexpr int STAGE_MAX = NG > 1 ? 5 : 3;
+    static constexpr int NSTAGE = STAGE_ROOM >= STAGE_MAX ? STAGE_MAX : (STAGE_ROOM >= 2 ? STAGE_ROOM : 2);
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int OFF_OWN = 0;
     static constexpr int OFF_OTH = OFF_OWN + MT::NOWN * OWN_TILE_BYTES;
     static constexpr int OFF_STAT = OFF_OTH + NSTAGE * OTH_STAGE_BYTES;         // [NSTAGE][4][TN] floats
-    static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [4][NSPLIT][128] floats
-    static constexpr int OFF_BAR = OFF_RED + 4 * NSPLIT * 128 * 4;
-    static constexpr int NBARS = 1 + 3 * NSTAGE + 6;
+    static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [2][NG * NSPLIT][128] floats
+    static constexpr int OFF_BAR = OFF_RED + 2 * NG * NSPLIT * 128 * 4;
+    static constexpr int NBARS = 1 + 3 * NSTAGE + 2 + 5 * NG;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag
     static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;                     // + alignment slack
     static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
@@ -169,12 +178,16 @@ __device__ __forceinline__ void store16_from_float(void* base, long long elem_of
 template <bool V> struct BoolTag { static constexpr bool value = V; };
 template <int V> struct IntTag { static constexpr int value = V; };
 
-template <int MODE, int DPAD, int TN, bool BF16>
-__global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN>::NTHREADS, 1)
+template <int MODE, int DPAD, int TN, bool BF16, int NG, int CW>
+__global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN, NG, CW>::NTHREADS, 1)
 sweep_kernel(const __grid_constant__ SweepParams p) {
-    using CFG = SweepConfig<MODE, DPAD, TN>;
+    using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
+    static_assert(CW == 16 || (CW == 32 && MODE != kFwd), "16 or 32 columns per pointwise thread");
+    constexpr bool PREFETCH = false;           // keep the next round's loads in flight while computing
+    constexpr int RW = (CW == 32) ? 16 : 8;    // columns per round of tensor-memory loads
+    static_assert(NG == 1 || MODE == kBwd2Row || MODE == kBwd2Col, "two groups: second backward only");
     using MT = ModeTraits<MODE>;
-    constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
+    constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, GP = CFG::GP, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
     constexpr bool COL = MT::COL;
     constexpr bool BWD2 = (MODE == kBwd2Row || MODE == kBwd2Col);
     constexpr float kLog2e = 1.4426950408889634f;
@@ -191,13 +204,15 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     const uint32_t bar_own = bar0;
     auto bar_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (1 + NSTAGE + s); };
-    const uint32_t bar_sc_full = bar0 + 8u * (1 + 2 * NSTAGE);
-    const uint32_t bar_sc_empty = bar_sc_full + 8;
-    const uint32_t bar_op_full = bar_sc_full + 16;
-    const uint32_t bar_op_empty = bar_sc_full + 24;
-    const uint32_t bar_done = bar_sc_full + 32;
-    const uint32_t bar_pw = bar_sc_full + 40;
-    auto bar_stat = [&](int s) { return bar_sc_full + 48u + 8u * s; };    // per-stage: row statistics staged
+    auto bar_stat = [&](int s) { return bar0 + 8u * (1 + 2 * NSTAGE + s); };     // per stage: row statistics staged
+    const uint32_t bar_done = bar0 + 8u * (1 + 3 * NSTAGE);
+    const uint32_t bar_pw_all = bar_done + 8;                                  // all pointwise threads
+    const uint32_t bar_grp0 = bar_done + 16;                                   // five barriers per group:
+    auto bar_sc_full = [&](int g) { return bar_grp0 + 40u * g; };             //   scores ready
+    auto bar_sc_empty = [&](int g) { return bar_grp0 + 40u * g + 8; };        //   scores read
+    auto bar_op_full = [&](int g) { return bar_grp0 + 40u * g + 16; };        //   operands written
+    auto bar_op_empty = [&](int g) { return bar_grp0 + 40u * g + 24; };       //   operands consumed
+    auto bar_pw = [&](int g) { return bar_grp0 + 40u * g + 32; };             //   the group's own threads
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -244,12 +259,15 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     if (tid == 0) {
         mbar_init(bar_own, 1);
         for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); mbar_init(bar_stat(s), 32); }
-        mbar_init(bar_sc_full, 1);
-        mbar_init(bar_sc_empty, NPW / 32);
-        mbar_init(bar_op_full, NPW / 32);
-        mbar_init(bar_op_empty, 1);
+        for (int g = 0; g < NG; ++g) {
+            mbar_init(bar_sc_full(g), 1);
+            mbar_init(bar_sc_empty(g), GP / 32);
+            mbar_init(bar_op_full(g), GP / 32);
+            mbar_init(bar_op_empty(g), 1);
+            mbar_init(bar_pw(g), GP / 32);
+        }
         mbar_init(bar_done, 1);
-        mbar_init(bar_pw, NPW / 32);
+        mbar_init(bar_pw_all, NPW / 32);
         misc[1] = 0;
         mbar_fence_init();
     }
@@ -261,8 +279,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = misc[0];
-    const uint32_t tmem_oper = tmem + CFG::SC_COLS;
-    const uint32_t tmem_out = tmem_oper + CFG::OPER_COLS;
+    // [scores of group 0 .. NG-1 | operands of group 0 .. NG-1 | output accumulators]
+    const uint32_t tmem_oper = tmem + NG * CFG::SC_COLS;
+    const uint32_t tmem_out = tmem_oper + NG * CFG::OPER_COLS;
 
     auto give_up = [&](int code) {
         misc[1] = 1;
@@ -365,7 +384,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             // score-shaped product: acc[128, NS*TN] (+)= own[slot_a] * other[slot_b .. slot_b+NS-1]^T.
             // NS = 2 takes two adjacent swept tiles as one 2*TN-row operand and fills two adjacent
             // accumulators with one instruction per K step (the own tile is read once, not twice).
-            auto score_mma = [&](auto ns_tag, int acc, int slot_a, int slot_b, uint32_t stage16, bool accumulate) {
+            auto score_mma = [&](auto ns_tag, uint32_t sc_base, int acc, int slot_a, int slot_b, uint32_t stage16, bool accumulate) {
                 constexpr int NS = decltype(ns_tag)::value;
                 constexpr uint32_t idesc = umma_idesc(fmt, fmt, NS * TN, false);
                 const uint32_t a = own16 + ((slot_a * CFG::OWN_TILE_BYTES) >> 4);
@@ -374,61 +393,63 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 for (int ks = 0; ks < DPAD / 16; ++ks) {
                     const uint32_t ao = ((ks / 4) * (128 * 128) + (ks % 4) * 32) >> 4;
                     const uint32_t bo = ((ks / 4) * (MT::NOTH * CFG::OTH_SUB_BYTES) + (ks % 4) * 32) >> 4;
-                    if (elect_one()) umma_ss_lo(tmem + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
+                    if (elect_one()) umma_ss_lo(sc_base + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
                 }
             };
             // output-shaped product: out[128, DPAD] (+)= operand[oper] * other[slot_b]; the operand is
             // read from tensor memory (8 columns per 16-element K step), the swept tile MN-major
             // from shared memory
-            auto out_mma = [&](int out, int oper, int slot_b, uint32_t stage16, bool accumulate) {
-                constexpr uint32_t idesc = umma_idesc(fmt, fmt, 64, true);
-                const uint32_t a = tmem_oper + oper * CFG::OPER_COLS_EACH;
-                const uint32_t b = stage16 + ((slot_b * CFG::OTH_SUB_BYTES) >> 4);
+            auto out_mma = [&](uint32_t op_base, int out, int oper, int slot_b, uint32_t stage16, bool accumulate) {
+                // all DPAD output columns in one instruction: at head dim 128 the second 64 columns come
+                // from the swept tensor's second sub-tile, one `leading byte offset` further on
+                constexpr uint32_t idesc = umma_idesc(fmt, fmt, DPAD, true);
+                constexpr uint32_t lbo16 = (KSUB > 1) ? ((MT::NOTH * CFG::OTH_SUB_BYTES) >> 4) : 1u;
+                const uint32_t a = op_base + oper * CFG::OPER_COLS_EACH;
+                const uint32_t b = (stage16 - 0x10000u) + (lbo16 << 16) + ((slot_b * CFG::OTH_SUB_BYTES) >> 4);
                 #pragma unroll
-                for (int db = 0; db < KSUB; ++db) {
-                    #pragma unroll
-                    for (int ks = 0; ks < TN / 16; ++ks) {
-                        if (elect_one())
-                            umma_ts_lo(tmem_out + out * DPAD + db * 64, a + ks * 8,
-                                       b + ((db * MT::NOTH * CFG::OTH_SUB_BYTES + ks * 2048) >> 4), idesc,
-                                       (accumulate || ks > 0) ? 1u : 0u);
-                    }
+                for (int ks = 0; ks < TN / 16; ++ks) {
+                    if (elect_one())
+                        umma_ts_lo(tmem_out + out * DPAD, a + ks * 8, b + ((ks * 2048) >> 4), idesc,
+                                   (accumulate || ks > 0) ? 1u : 0u);
                 }
             };
             using NS1 = IntTag<1>;
             using NS2 = IntTag<2>;
 
             BOB_PH_DECL
-            // scores of iteration `it`, whose swept tiles sit in pipeline stage `stage` (use number `round`)
+            // scores of iteration `it` (group it % NG, that group's tile number it / NG), whose swept
+            // tiles sit in pipeline stage `stage` (use number `round`)
             auto issue_scores = [&](int it, int stage, int round) -> bool {
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
+                const int g = it % NG, j = it / NG;
+                const uint32_t sc = tmem + g * CFG::SC_COLS;
                 BOB_PH(7)
                 if (!__all_sync(0xffffffffu, mbar_wait(bar_full(stage), round & 1))) { give_up(kStatusTimeoutMma); return false; }
                 BOB_PH(0)
-                if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_sc_empty, (it - 1) & 1))) { give_up(kStatusTimeoutMma); return false; }
+                if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_sc_empty(g), (j - 1) & 1))) { give_up(kStatusTimeoutMma); return false; }
                 BOB_PH(1)
                 tc_fence_after_sync();
                 if constexpr (MODE == kFwd) {
-                    score_mma(NS1{}, 0, 0, 0, s, false);
+                    score_mma(NS1{}, sc, 0, 0, 0, s, false);
                 } else if constexpr (MODE == kBwd1Row || MODE == kBwd1Col) {
-                    score_mma(NS1{}, 0, 0, 0, s, false);     // S  = Q K^T      | S^T  = K Q^T
-                    score_mma(NS1{}, 1, 1, 1, s, false);     // dP = dO V^T     | dP^T = V dO^T
+                    score_mma(NS1{}, sc, 0, 0, 0, s, false);     // S  = Q K^T      | S^T  = K Q^T
+                    score_mma(NS1{}, sc, 1, 1, 1, s, false);     // dP = dO V^T     | dP^T = V dO^T
                 } else if constexpr (MODE == kBwd2Row) {
                     // own: Q, dO, uQ;  swept: K, uK, V, uV;  accumulators: S, F, dP, C
-                    if (p.has_uk) score_mma(NS2{}, 0, 0, 0, s, false);      // S | F  = Q [K; uK]^T
-                    else          score_mma(NS1{}, 0, 0, 0, s, false);      // S      = Q K^T
-                    if (p.has_uq) score_mma(NS1{}, 1, 2, 0, s, p.has_uk);   // F     += uQ K^T
-                    if (p.has_uv) score_mma(NS2{}, 2, 1, 2, s, false);      // dP | C = dO [V; uV]^T
-                    else          score_mma(NS1{}, 2, 1, 2, s, false);      // dP     = dO V^T
+                    if (p.has_uk) score_mma(NS2{}, sc, 0, 0, 0, s, false);      // S | F  = Q [K; uK]^T
+                    else          score_mma(NS1{}, sc, 0, 0, 0, s, false);      // S      = Q K^T
+                    if (p.has_uq) score_mma(NS1{}, sc, 1, 2, 0, s, p.has_uk);   // F     += uQ K^T
+                    if (p.has_uv) score_mma(NS2{}, sc, 2, 1, 2, s, false);      // dP | C = dO [V; uV]^T
+                    else          score_mma(NS1{}, sc, 2, 1, 2, s, false);      // dP     = dO V^T
                 } else {
                     // own: K, V, uK, uV;  swept: Q, uQ, dO;  accumulators: S^T, F^T, dP^T, C^T
-                    if (p.has_uq) score_mma(NS2{}, 0, 0, 0, s, false);      // S^T | F^T = K [Q; uQ]^T
-                    else          score_mma(NS1{}, 0, 0, 0, s, false);      // S^T       = K Q^T
-                    if (p.has_uk) score_mma(NS1{}, 1, 2, 0, s, p.has_uq);   // F^T      += uK Q^T
-                    score_mma(NS1{}, 2, 1, 2, s, false);                    // dP^T      = V dO^T
-                    if (p.has_uv) score_mma(NS1{}, 3, 3, 2, s, false);      // C^T       = uV dO^T
+                    if (p.has_uq) score_mma(NS2{}, sc, 0, 0, 0, s, false);      // S^T | F^T = K [Q; uQ]^T
+                    else          score_mma(NS1{}, sc, 0, 0, 0, s, false);      // S^T       = K Q^T
+                    if (p.has_uk) score_mma(NS1{}, sc, 1, 2, 0, s, p.has_uq);   // F^T      += uK Q^T
+                    score_mma(NS1{}, sc, 2, 1, 2, s, false);                    // dP^T      = V dO^T
+                    if (p.has_uv) score_mma(NS1{}, sc, 3, 3, 2, s, false);      // C^T       = uV dO^T
                 }
-                if (elect_one()) umma_commit(bar_sc_full);
+                if (elect_one()) umma_commit(bar_sc_full(g));
                 BOB_PH(2)
                 return true;
             };
@@ -444,32 +465,34 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
                 const bool has_out = (MODE != kFwd) || it >= T;
                 if (has_out) {
+                    const int g = it % NG;
+                    const uint32_t ob = tmem_oper + g * CFG::OPER_COLS;
                     BOB_PH(7)
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar_op_full, n_out & 1))) { give_up(kStatusTimeoutMma); break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar_op_full(g), (n_out / NG) & 1))) { give_up(kStatusTimeoutMma); break; }
                     BOB_PH(3)
                     tc_fence_after_sync();
                     const bool acc = n_out > 0;
                     if constexpr (MODE == kFwd) {
-                        out_mma(0, 0, 1, s, acc);                       // O += P V
+                        out_mma(ob, 0, 0, 1, s, acc);                       // O += P V
                     } else if constexpr (MODE == kBwd1Row) {
-                        out_mma(0, 0, 0, s, acc);                       // dQ += dS K
-                        if (p.pk) out_mma(1, 1, 0, s, acc);             // PK += P K
+                        out_mma(ob, 0, 0, 0, s, acc);                       // dQ += dS K
+                        if (p.pk) out_mma(ob, 1, 1, 0, s, acc);             // PK += P K
                     } else if constexpr (MODE == kBwd1Col) {
-                        out_mma(0, 1, 0, s, acc);                       // dK += dS^T Q
-                        out_mma(1, 0, 1, s, acc);                       // dV += P^T dO
+                        out_mma(ob, 0, 1, 0, s, acc);                       // dK += dS^T Q
+                        out_mma(ob, 1, 0, 1, s, acc);                       // dV += P^T dO
                     } else if constexpr (MODE == kBwd2Row) {
                         // operands: P, P*F, P*T, dS;  swept: K, uK, V, uV;  outputs: dObar, Omega
-                        if (p.has_uv) out_mma(0, 0, 3, s, acc);         // dObar += P uV
-                        out_mma(0, 1, 2, s, acc || p.has_uv);           // dObar += (P*F) V
-                        out_mma(1, 2, 0, s, acc);                       // Omega += (P*T) K
-                        if (p.has_uk) out_mma(1, 3, 1, s, true);        // Omega += dS uK
+                        if (p.has_uv) out_mma(ob, 0, 0, 3, s, acc);         // dObar += P uV
+                        out_mma(ob, 0, 1, 2, s, acc || p.has_uv);           // dObar += (P*F) V
+                        out_mma(ob, 1, 2, 0, s, acc);                       // Omega += (P*T) K
+                        if (p.has_uk) out_mma(ob, 1, 3, 1, s, true);        // Omega += dS uK
                     } else {
                         // operands: Sbar^T, dS^T, (P*(F-alpha))^T;  outputs: Kbar, Vbar
-                        out_mma(0, 0, 0, s, acc);                       // Kbar += Sbar^T Q
-                        if (p.has_uq) out_mma(0, 1, 1, s, true);        // Kbar += dS^T uQ
-                        out_mma(1, 2, 2, s, acc);                       // Vbar += (P*(F-alpha))^T dO
+                        out_mma(ob, 0, 0, 0, s, acc);                       // Kbar += Sbar^T Q
+                        if (p.has_uq) out_mma(ob, 0, 1, 1, s, true);        // Kbar += dS^T uQ
+                        out_mma(ob, 1, 2, 2, s, acc);                       // Vbar += (P*(F-alpha))^T dO
                     }
-                    if (elect_one()) umma_commit(bar_op_empty);
+                    if (elect_one()) umma_commit(bar_op_empty(g));
                     ++n_out;
                 }
                 if (elect_one()) umma_commit(bar_empty(stage));
@@ -482,24 +505,27 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
     } else {
         // =========================== pointwise threads =======================================
-        const int row = tid & 127;               // own row inside the tile == tensor-memory lane
-        const int sp = tid >> 7;                 // which 16-column slice of every score tile
-        const int col0 = sp * 16;                // my first column inside a swept tile
+        const int grp = tid / GP;                // pointwise group: takes iterations grp, grp + NG, ...
+        const int gtid = tid % GP;
+        const int row = gtid & 127;              // own row inside the tile == tensor-memory lane
+        const int sp = gtid >> 7;                // which 16-column slice of every score tile
+        const int col0 = sp * CW;                // my first column inside a swept tile
         const int own_idx = own0 + row;
         const bool own_ok = own_idx < n_own;
-        const uint32_t tlane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        const uint32_t tlane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);   // my lane, column 0
+        const uint32_t tsc = tlane + grp * CFG::SC_COLS;                                  // my group's scores
         const float c_exp = p.scale * kLog2e;
         const long long row_stat = ((long long)batch * p.Hq + head) * p.Nq + own_idx;   // row-owned only
 
         // where my 16 columns (8 packed words) of operand k go in tensor memory
-        const uint32_t op_taddr = tlane + CFG::SC_COLS + (col0 >> 1);
+        const uint32_t op_taddr = tlane + NG * CFG::SC_COLS + grp * CFG::OPER_COLS + (col0 >> 1);
 
         // Synchronise the pointwise threads through an mbarrier so that the wait is bounded.
         uint32_t pw_phase = 0;
         auto pw_sync = [&]() -> bool {
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_pw);
-            const bool r = __all_sync(0xffffffffu, mbar_wait(bar_pw, pw_phase));
+            if (lane == 0) mbar_arrive(bar_pw(grp));
+            const bool r = __all_sync(0xffffffffu, mbar_wait(bar_pw(grp), pw_phase));
             pw_phase ^= 1u;
             if (!r) give_up(kStatusTimeoutPw);
             return r;
@@ -583,16 +609,17 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 // the swept tile's row statistics were staged by the producer warp
                 if (!pw_wait(bar_stat(stage), round & 1)) return false;
             }
-            if (!pw_wait(bar_sc_full, it & 1)) return false;
+            if (!pw_wait(bar_sc_full(grp), (it / NG) & 1)) return false;
             BOB_PH(0)
             tc_fence_after_sync();
 
             // ---- which of my 16 columns are unmasked: bits [mlo, mhi] of vmask ----------------
             // dist = query position - key position; unmasked iff in range and, when causal,
             // 0 <= dist (< window)
-            uint32_t vmask = 0xFFFFu;
+            constexpr uint32_t kAllCols = (CW == 32) ? 0xFFFFFFFFu : 0xFFFFu;
+            uint32_t vmask = kAllCols;
             if constexpr (!FULL) {
-                int mlo = 0, mhi = min(15, n_oth - (oth0 + col0) - 1);
+                int mlo = 0, mhi = min(CW - 1, n_oth - (oth0 + col0) - 1);
                 if (p.is_causal) {
                     if constexpr (!COL) {
                         const int d0 = own_idx + doff - (oth0 + col0);       // dist falls with the column
@@ -604,18 +631,18 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         if (p.window > 0) mhi = min(mhi, p.window - 1 - d0);
                     }
                 }
-                vmask = (own_ok && mhi >= mlo) ? ((0xFFFFu >> (15 - mhi)) & (0xFFFFu << mlo)) : 0u;
+                vmask = (own_ok && mhi >= mlo) ? ((kAllCols >> (CW - 1 - mhi)) & (kAllCols << mlo)) : 0u;
             }
 
             float s_[16];
-            if constexpr (MODE == kFwd) tmem_ld16(tlane + 0 * TN + col0, s_);
-            else                        tmem_ld8(tlane + 0 * TN + col0, s_);
+            if constexpr (MODE == kFwd) tmem_ld16(tsc + 0 * TN + col0, s_);
+            else                        tmem_ld8(tsc + 0 * TN + col0, s_);
 
             if constexpr (MODE == kFwd) {
                 tmem_wait_ld();
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_sc_empty);
+                if (lane == 0) mbar_arrive(bar_sc_empty(grp));
                 if (outer == 0) {
                     float mx = run_max;
                     #pragma unroll
@@ -641,48 +668,63 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     }
                     w0[c2] = pack2<BF16>(a, b);
                 }
-                if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) return false;
+                if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
                 tmem_st8(op_taddr, w0);
             } else {
                 // accumulator order: S, dP (first backward) or S, F, dP, C (second backward).
-                // My 16 columns are taken in two halves of 8 to bound the live registers; the
-                // score accumulators are handed back as soon as the second half is loaded.
+                // My CW columns are taken in rounds of 8 to bound the live registers; the score
+                // accumulators are handed back as soon as the last round is loaded.
+                constexpr int R = CW / RW;
                 const float2 cexp2 = make_float2(c_exp, c_exp);
                 const float2 scale2 = make_float2(p.scale, p.scale);
                 const bool has_f = BWD2 && (p.has_uq || p.has_uk);
                 const bool has_c = BWD2 && p.has_uv;
-                uint32_t w0[8], w1[8], w2[8], w3[8];
-                #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int cb = col0 + 8 * half;
-                    float dp_[8], f_[8], cc_[8];
-                    if (half == 1) tmem_ld8(tlane + 0 * TN + cb, s_);
-                    tmem_ld8(tlane + (BWD2 ? 2 : 1) * TN + cb, dp_);
+                uint32_t w0[CW / 2], w1[CW / 2], w2[CW / 2], w3[CW / 2];
+                float in_s[2][RW], in_dp[2][RW], in_f[2][RW], in_c[2][RW];
+                auto issue_loads = [&](int r, int b) {
+                    const int cb = col0 + RW * r;
+                    auto ld = [&](uint32_t addr, float* dst) {
+                        if constexpr (RW == 16) tmem_ld16(addr, dst); else tmem_ld8(addr, dst);
+                    };
+                    ld(tsc + 0 * TN + cb, in_s[b]);
+                    ld(tsc + (BWD2 ? 2 : 1) * TN + cb, in_dp[b]);
                     if constexpr (BWD2) {
-                        if (has_f) tmem_ld8(tlane + 1 * TN + cb, f_);
-                        if (has_c) tmem_ld8(tlane + 3 * TN + cb, cc_);
+                        if (has_f) ld(tsc + 1 * TN + cb, in_f[b]);
+                        if (has_c) ld(tsc + 3 * TN + cb, in_c[b]);
                     }
+                };
+                issue_loads(0, 0);
+                #pragma unroll
+                for (int half = 0; half < R; ++half) {            // `half` = round of RW columns
+                    const int cb = col0 + RW * half;
+                    const int b = PREFETCH ? (half & 1) : 0;
                     tmem_wait_ld();
                     BOB_PH(1)
-                    if (half == 1) {
+                    if (half + 1 < R) {
+                        if constexpr (PREFETCH) issue_loads(half + 1, (half + 1) & 1);
+                    } else {
                         tc_fence_before_sync();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_sc_empty);
+                        if (lane == 0) mbar_arrive(bar_sc_empty(grp));
                     }
+                    float* s_ = in_s[b];
+                    float* dp_ = in_dp[b];
+                    float* f_ = in_f[b];
+                    float* cc_ = in_c[b];
                     if constexpr (BWD2) {
                         if (!has_f) {
                             #pragma unroll
-                            for (int c = 0; c < 8; ++c) f_[c] = 0.f;
+                            for (int c = 0; c < RW; ++c) f_[c] = 0.f;
                         }
                         if (!has_c) {
                             #pragma unroll
-                            for (int c = 0; c < 8; ++c) cc_[c] = 0.f;
+                            for (int c = 0; c < RW; ++c) cc_[c] = 0.f;
                         }
                     }
                     // negated statistics of these columns (column-owned modes), four columns per load
                     const float4* sb4 = reinterpret_cast<const float4*>(stat_buf + stage * 4 * TN + cb);
                     #pragma unroll
-                    for (int c4 = 0; c4 < 2; ++c4) {
+                    for (int c4 = 0; c4 < RW / 4; ++c4) {
                         float4 q_l2, q_dl, q_al, q_ec;
                         if constexpr (COL) {
                             q_l2 = sb4[c4]; q_dl = sb4[TN / 4 + c4];
@@ -691,8 +733,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             const int c = 4 * c4 + 2 * h;          // columns c, c + 1 of this half
-                            const int wi = 4 * half + (c >> 1);    // packed word index among my 16 columns
-                            const int mc = 8 * half + c;           // bit index in vmask
+                            const int wi = (RW / 2) * half + (c >> 1);   // packed word index among my CW columns
+                            const int mc = RW * half + c;                // bit index in vmask
                             float2 nl2, ndl, nal, nec;
                             if constexpr (COL) {
                                 nl2 = h ? make_float2(q_l2.z, q_l2.w) : make_float2(q_l2.x, q_l2.y);
@@ -745,26 +787,37 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                             }
                         }
                     }
+                    if constexpr (!PREFETCH) {
+                        if (half + 1 < R) issue_loads(half + 1, 0);
+                    }
                 }
                 BOB_PH(2)
-                if (n_op > 0 && !pw_wait(bar_op_empty, (n_op - 1) & 1)) return false;
+                if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
                 BOB_PH(3)
-                tmem_st8(op_taddr + 0 * CFG::OPER_COLS_EACH, w0);
-                if constexpr (MT::NOPER > 1) tmem_st8(op_taddr + 1 * CFG::OPER_COLS_EACH, w1);
-                if constexpr (MT::NOPER > 2) tmem_st8(op_taddr + 2 * CFG::OPER_COLS_EACH, w2);
-                if constexpr (MT::NOPER > 3) tmem_st8(op_taddr + 3 * CFG::OPER_COLS_EACH, w3);
+                #pragma unroll
+                for (int h = 0; h < CW / 16; ++h) {
+                    tmem_st8(op_taddr + 0 * CFG::OPER_COLS_EACH + 8 * h, w0 + 8 * h);
+                    if constexpr (MT::NOPER > 1) tmem_st8(op_taddr + 1 * CFG::OPER_COLS_EACH + 8 * h, w1 + 8 * h);
+                    if constexpr (MT::NOPER > 2) tmem_st8(op_taddr + 2 * CFG::OPER_COLS_EACH + 8 * h, w2 + 8 * h);
+                    if constexpr (MT::NOPER > 3) tmem_st8(op_taddr + 3 * CFG::OPER_COLS_EACH + 8 * h, w3 + 8 * h);
+                }
             }
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_op_full);
+            if (lane == 0) mbar_arrive(bar_op_full(grp));
             ++n_op;
             BOB_PH(4)
             return true;
         };
 
         int tile = t_lo, outer = 0, stage = 0, round = 0;
-        for (int it = 0; ok && it < total; ++it) {
+        auto advance = [&]() {
+            if (++tile == t_hi) { tile = t_lo; ++outer; }
+            if (++stage == NSTAGE) { stage = 0; ++round; }
+        };
+        for (int k = 0; k < grp; ++k) advance();
+        for (int it = grp; ok && it < total; it += NG) {
             // is the whole 128 x TN tile pair unmasked and inside both tensors?  (uniform per CTA)
             const int oth0 = tile * TN;
             bool full = (own0 + 127 < n_own) && (oth0 + TN <= n_oth);
@@ -775,8 +828,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             }
             ok = full ? tile_body(BoolTag<true>{}, it, tile, outer, stage, round)
                       : tile_body(BoolTag<false>{}, it, tile, outer, stage, round);
-            if (++tile == t_hi) { tile = t_lo; ++outer; }
-            if (++stage == NSTAGE) { stage = 0; ++round; }
+            #pragma unroll
+            for (int k = 0; k < NG; ++k) advance();
         }
 
         BOB_PH_FLUSH(0, tid == 0)
@@ -787,27 +840,32 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         float alpha = 0.f, ecirc = 0.f;
         ok = __all_sync(0xffffffffu, ok);
         if constexpr (MODE == kBwd2Row) {
-            red_buf[sp * 128 + row] = acc_a.x + acc_a.y;
-            red_buf[(NSPLIT + sp) * 128 + row] = acc_b.x + acc_b.y;
-            if (ok) ok = pw_sync();
+            constexpr int NPART = NG * NSPLIT;          // every pointwise thread of my row holds a partial sum
+            red_buf[(grp * NSPLIT + sp) * 128 + row] = acc_a.x + acc_a.y;
+            red_buf[(NPART + grp * NSPLIT + sp) * 128 + row] = acc_b.x + acc_b.y;
+            if (ok) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_pw_all);
+                ok = pw_wait(bar_pw_all, 0);
+            }
             #pragma unroll
-            for (int k = 0; k < NSPLIT; ++k) { alpha += red_buf[k * 128 + row]; ecirc += red_buf[(NSPLIT + k) * 128 + row]; }
-            if (ok && sp == 0 && own_ok) { p.alpha[row_stat] = alpha; p.ecirc[row_stat] = ecirc; }
+            for (int k = 0; k < NPART; ++k) { alpha += red_buf[k * 128 + row]; ecirc += red_buf[(NPART + k) * 128 + row]; }
+            if (ok && grp == 0 && sp == 0 && own_ok) { p.alpha[row_stat] = alpha; p.ecirc[row_stat] = ecirc; }
         }
         if (ok && total > 0) ok = pw_wait(bar_done, 0);
         tc_fence_after_sync();
         if (ok) {
-            constexpr int DC = DPAD / NSPLIT;
+            constexpr int DC = DPAD / (NSPLIT * NG);    // output columns per pointwise thread
             const int res_heads = COL ? p.Hkv : p.Hq;
             const long long res_off = (((long long)batch * res_heads + head) * n_own + own_idx) * p.D;
             #pragma unroll 1
             for (int c = 0; c < DC; c += 16) {
-                const int col = sp * DC + c;
+                const int col = (grp * NSPLIT + sp) * DC + c;
                 if (col >= p.D) break;
                 float a0[16], a1[16];
                 if (total > 0) {
-                    tmem_ld16(tlane + CFG::SC_COLS + CFG::OPER_COLS + 0 * DPAD + col, a0);
-                    if constexpr (MT::NOUT > 1) tmem_ld16(tlane + CFG::SC_COLS + CFG::OPER_COLS + 1 * DPAD + col, a1);
+                    tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 0 * DPAD + col, a0);
+                    if constexpr (MT::NOUT > 1) tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 1 * DPAD + col, a1);
                     tmem_wait_ld();
                 } else {
                     #pragma unroll
