@@ -307,16 +307,61 @@ def main():
     h2d = sum(t.numel() * t.element_size() for t in pin.values())
     d2h = sum(t.numel() * t.element_size() for t in pin_out.values())
 
-    def e2e_step():
-        for n in names_in:
-            stage[n].copy_(pin[n], non_blocking=True)
-        bwd2(stage)
-        for n in res:
-            pin_out[n].copy_(res[n], non_blocking=True)
+    # Steps are pipelined over three streams with two sets of device buffers: while step i computes,
+    # step i+1's inputs cross PCIe and step i-1's results go back.  Every step still copies all of
+    # its inputs from pinned host memory and all of its results back to pinned host memory.
+    s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    stage2 = [stage, {n: torch.empty_like(d[n]) for n in names_in}]
+    res2 = [res, {n: torch.empty_like(t) for n, t in res.items()}]
+    pin_out2 = [pin_out, {n: torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for n, t in res.items()}]
 
-    e2e_steps = max(3, min(args.steps, 10))
-    ems, _ = timed_steps(e2e_step, 2, e2e_steps)
-    e2e_ms = torch.tensor([sum(ems)], dtype=torch.float64, device=dev)
+    def bwd2_on(src, dst, cuda_stream):
+        rc = lib.bob_sm100_bwd2(ctypes.byref(g), vp(src["q"]), vp(src["k"]), vp(src["v"]), vp(src["out"]),
+                                vp(src["lse"]), vp(src["delta"]), vp(src["pk"]), vp(src["dO"]), vp(src["dQ"]),
+                                vp(src["uQ"]), vp(src["uK"]), vp(src["uV"]), vp(dst["Qbar"]), vp(dst["Kbar"]),
+                                vp(dst["Vbar"]), vp(dst["dObar"]), vp(ws), ctypes.c_void_p(cuda_stream))
+        _lib.check(rc, "bob_sm100_bwd2")
+
+    def e2e_run(n_steps):
+        ev_in = [None, None]; ev_cmp = [None, None]; ev_out = [None, None]
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for st_ in (s_in, s_cmp, s_out):
+            st_.wait_event(start)
+        for i in range(n_steps):
+            s = i & 1
+            with torch.cuda.stream(s_in):
+                if ev_cmp[s] is not None:
+                    s_in.wait_event(ev_cmp[s])           # step i-2 no longer reads this input set
+                for n in names_in:
+                    stage2[s][n].copy_(pin[n], non_blocking=True)
+                ev_in[s] = torch.cuda.Event(); ev_in[s].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in[s])
+                if ev_out[s] is not None:
+                    s_cmp.wait_event(ev_out[s])          # step i-2's results have left this result set
+                bwd2_on(stage2[s], res2[s], s_cmp.cuda_stream)
+                ev_cmp[s] = torch.cuda.Event(); ev_cmp[s].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[s])
+                for n in res:
+                    pin_out2[s][n].copy_(res2[s][n], non_blocking=True)
+                ev_out[s] = torch.cuda.Event(); ev_out[s].record(s_out)
+        for st_ in (s_in, s_cmp, s_out):
+            stream.wait_stream(st_)
+        end.record(stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        return start.elapsed_time(end)
+
+    e2e_steps = max(4, min(args.steps, 12))
+    e2e_run(3)
+    e2e_total = e2e_run(e2e_steps)
+    e2e_ms = torch.tensor([e2e_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_value = flops_job / (e2e_ms.item() / e2e_steps * 1e-3) / 1e12
@@ -359,7 +404,9 @@ def main():
                      "kernel": "second backward = row-owned kernel + column-owned kernel",
                      "kernel_ms": kernel_ms},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps},
+                "steps": e2e_steps, "ms_per_step": e2e_ms.item() / e2e_steps,
+                "how": "pinned host -> device -> bob_sm100_bwd2 -> pinned host every step; steps pipelined "
+                       "over copy-in / compute / copy-out streams; inputs per step exceed L2"},
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
         "wall_s_timed_region": wall,

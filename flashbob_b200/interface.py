@@ -190,6 +190,10 @@ class SDPAWithBoB(Function):
 
     @staticmethod
     def forward(ctx, q, k, v, q_offset, k_offset, is_causal, window_size, scale):
+        # An undefined cotangent (the second differentiation of leaf-cotangent protocols reaches this
+        # node with nothing to propagate) must not be turned into a tensor of zeros and pushed
+        # through a pointless first backward.
+        ctx.set_materialize_grads(False)
         q_offset = 0 if q_offset is None else int(q_offset)
         k_offset = 0 if k_offset is None else int(k_offset)
         geom = dict(is_causal=is_causal, window_size=window_size, q_offset=q_offset,
@@ -201,6 +205,8 @@ class SDPAWithBoB(Function):
 
     @staticmethod
     def backward(ctx, dO):
+        if dO is None:
+            return (None,) * 8
         q, k, v, out, lse = ctx.saved_tensors
         g = ctx.geom
         if not torch.is_grad_enabled():
