@@ -91,8 +91,10 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
     return cudaGetLastError() == cudaSuccess ? 0 : kErrLaunch;
 }
 
-// Tile table.  Head dim <= 64: 64-wide swept tiles everywhere; the second backward gives each
-// pointwise thread 32 columns (256 threads with room to prefetch tensor-memory loads).  Head dim
+// Tile table.  Head dim <= 64: 64-wide swept tiles and 32 columns per pointwise thread everywhere.
+// Forward and first backward need few accumulators, so tensor memory holds two sets of them and two
+// pointwise groups (2 x 256 threads) take the swept tiles in turn; the second backward has one group
+// of 256 threads with 168 registers each.  Head dim
 // 128: 64-wide tiles except the second backward, whose four score accumulators and three or four
 // operands leave tensor memory (512 columns) room for 32-wide tiles only.
 template <int MODE, bool BF16>
@@ -101,7 +103,7 @@ static int dispatch(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* 
     constexpr bool kSecond = (MODE == kBwd2Row || MODE == kBwd2Col);
     if (g->D <= 64) {
         if constexpr (kSecond) return launch_sweep<MODE, 64, 64, BF16, 1, 32>(g, prm, tensors, stream);
-        else                   return launch_sweep<MODE, 64, 64, BF16>(g, prm, tensors, stream);
+        else                   return launch_sweep<MODE, 64, 64, BF16, 2, 32>(g, prm, tensors, stream);
     }
     if constexpr (kSecond) return launch_sweep<MODE, 128, 32, BF16>(g, prm, tensors, stream);
     else                   return launch_sweep<MODE, 128, 64, BF16>(g, prm, tensors, stream);

@@ -121,11 +121,11 @@ struct SweepConfig {
     static constexpr int TMEM_NEED = NG * (SC_COLS + OPER_COLS) + OUT_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
     static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
-    // as many stages of swept tiles as shared memory allows, between 2 and 3 (5 with two groups,
-    // whose tiles are half as wide): the TMA latency of a tile hides behind the tiles before it
+    // as many stages of swept tiles as shared memory allows, between 2 and 6: the TMA latency of a
+    // tile (~2 us) hides behind the tiles before it
     static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + 16 * 1024;
     static constexpr int STAGE_ROOM = (232448 - FIXED_BYTES) / OTH_STAGE_BYTES;
-    static constexpr int STAGE_MAX = NG > 1 ? 5 : 3;
+    static constexpr int STAGE_MAX = 6;
     static constexpr int NSTAGE = STAGE_ROOM >= STAGE_MAX ? STAGE_MAX : (STAGE_ROOM >= 2 ? STAGE_ROOM : 2);
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int OFF_OWN = 0;
@@ -182,10 +182,9 @@ template <int MODE, int DPAD, int TN, bool BF16, int NG, int CW>
 __global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN, NG, CW>::NTHREADS, 1)
 sweep_kernel(const __grid_constant__ SweepParams p) {
     using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
-    static_assert(CW == 16 || (CW == 32 && MODE != kFwd), "16 or 32 columns per pointwise thread");
+    static_assert(CW == 16 || CW == 32, "16 or 32 columns per pointwise thread");
     constexpr bool PREFETCH = false;           // keep the next round's loads in flight while computing
     constexpr int RW = (CW == 32) ? 16 : 8;    // columns per round of tensor-memory loads
-    static_assert(NG == 1 || MODE == kBwd2Row || MODE == kBwd2Col, "two groups: second backward only");
     using MT = ModeTraits<MODE>;
     constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, GP = CFG::GP, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
     constexpr bool COL = MT::COL;
@@ -569,7 +568,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             #pragma unroll
             for (int k = 0; k < NSPLIT; ++k) dlt += red_buf[k * 128 + row];
             ok = ok && pw_sync();
-            if (sp == 0 && own_ok) p.delta[row_stat] = dlt;
+            if (grp == 0 && sp == 0 && own_ok) p.delta[row_stat] = dlt;
             ndlt = -dlt;
             if (own_ok) nL2 = -p.lse[row_stat] * kLog2e;
         }
@@ -578,6 +577,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
 
         int n_op = 0;                            // operand rounds written so far
+        bool fwd_combined = false;               // forward: first-sweep statistics already combined
         BOB_PH_DECL
 
         // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
@@ -586,21 +586,27 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             const int oth0 = tile * TN;
 
             if constexpr (MODE == kFwd) {
-                if (outer == 1 && it == T) {
-                    // between the two sweeps: combine the slices' (max, sum) into the row's lse
-                    red_buf[sp * 128 + row] = run_max;
-                    red_buf[(NSPLIT + sp) * 128 + row] = run_sum;
-                    if (!pw_sync()) return false;
+                if (outer == 1 && !fwd_combined) {
+                    // between the two sweeps: combine every slice's (max, sum) into the row's lse.
+                    // Each pointwise thread of the CTA arrives once: here, before its first tile of
+                    // the second sweep, or after its loop if it has no such tile.
+                    constexpr int NPART = NG * NSPLIT;
+                    red_buf[(grp * NSPLIT + sp) * 128 + row] = run_max;
+                    red_buf[(NPART + grp * NSPLIT + sp) * 128 + row] = run_sum;
+                    fwd_combined = true;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_pw_all);
+                    if (!pw_wait(bar_pw_all, 0)) return false;
                     float m = -1e30f;
                     #pragma unroll
-                    for (int k = 0; k < NSPLIT; ++k) m = fmaxf(m, red_buf[k * 128 + row]);
+                    for (int k = 0; k < NPART; ++k) m = fmaxf(m, red_buf[k * 128 + row]);
                     float l = 0.f;
                     #pragma unroll
-                    for (int k = 0; k < NSPLIT; ++k)
-                        l += red_buf[(NSPLIT + k) * 128 + row] * fast_exp2(red_buf[k * 128 + row] - m);
+                    for (int k = 0; k < NPART; ++k)
+                        l += red_buf[(NPART + k) * 128 + row] * fast_exp2(red_buf[k * 128 + row] - m);
                     const float L2 = (l > 0.f) ? m + log2f(l) : INFINITY;
                     nL2 = -L2;
-                    if (sp == 0 && own_ok) p.lse[row_stat] = (l > 0.f) ? L2 * kLn2 : -INFINITY;
+                    if (it == T && sp == 0 && own_ok) p.lse[row_stat] = (l > 0.f) ? L2 * kLn2 : -INFINITY;
                 }
             }
 
@@ -634,11 +640,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 vmask = (own_ok && mhi >= mlo) ? ((kAllCols >> (CW - 1 - mhi)) & (kAllCols << mlo)) : 0u;
             }
 
-            float s_[16];
-            if constexpr (MODE == kFwd) tmem_ld16(tsc + 0 * TN + col0, s_);
-            else                        tmem_ld8(tsc + 0 * TN + col0, s_);
-
             if constexpr (MODE == kFwd) {
+                float s_[CW];
+                #pragma unroll
+                for (int h = 0; h < CW / 16; ++h) tmem_ld16(tsc + col0 + 16 * h, s_ + 16 * h);
                 tmem_wait_ld();
                 tc_fence_before_sync();
                 __syncwarp();
@@ -646,20 +651,20 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 if (outer == 0) {
                     float mx = run_max;
                     #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
+                    for (int c = 0; c < CW; ++c) {
                         s_[c] = (FULL || ((vmask >> c) & 1u)) ? s_[c] * c_exp : -1e30f;
                         mx = fmaxf(mx, s_[c]);
                     }
                     float sum = run_sum * fast_exp2(run_max - mx);
                     #pragma unroll
-                    for (int c = 0; c < 16; ++c)
+                    for (int c = 0; c < CW; ++c)
                         sum += (FULL || ((vmask >> c) & 1u)) ? fast_exp2(s_[c] - mx) : 0.f;
                     run_max = mx; run_sum = sum;
                     return true;
                 }
-                uint32_t w0[8];
+                uint32_t w0[CW / 2];
                 #pragma unroll
-                for (int c2 = 0; c2 < 8; ++c2) {
+                for (int c2 = 0; c2 < CW / 2; ++c2) {
                     float a = fast_exp2(fmaf(s_[2 * c2], c_exp, nL2));
                     float b = fast_exp2(fmaf(s_[2 * c2 + 1], c_exp, nL2));
                     if constexpr (!FULL) {
@@ -669,7 +674,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     w0[c2] = pack2<BF16>(a, b);
                 }
                 if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
-                tmem_st8(op_taddr, w0);
+                #pragma unroll
+                for (int h = 0; h < CW / 16; ++h) tmem_st8(op_taddr + 8 * h, w0 + 8 * h);
             } else {
                 // accumulator order: S, dP (first backward) or S, F, dP, C (second backward).
                 // My CW columns are taken in rounds of 8 to bound the live registers; the score
@@ -835,7 +841,14 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         BOB_PH_FLUSH(0, tid == 0)
         // ---- epilogue ------------------------------------------------------------------------
         if constexpr (MODE == kFwd) {
-            if (total == 0 && sp == 0 && own_ok) p.lse[row_stat] = -INFINITY;
+            if (total == 0 && grp == 0 && sp == 0 && own_ok) p.lse[row_stat] = -INFINITY;
+            if (total > 0 && !fwd_combined) {
+                constexpr int NPART = NG * NSPLIT;
+                red_buf[(grp * NSPLIT + sp) * 128 + row] = run_max;
+                red_buf[(NPART + grp * NSPLIT + sp) * 128 + row] = run_sum;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_pw_all);
+            }
         }
         float alpha = 0.f, ecirc = 0.f;
         ok = __all_sync(0xffffffffu, ok);
