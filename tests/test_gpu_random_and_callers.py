@@ -1,0 +1,137 @@
+"""Randomised geometries against the oracle, and caller-level use: layout adapters and a
+Hessian-vector product over the parameters of a small attention block."""
+
+import random
+
+import pytest
+import torch
+
+import bob
+from flashbob_b200 import adapters, interface, ops
+from oracle import bob_oracle as O
+
+pytestmark = pytest.mark.gpu
+BF16, FP16 = torch.bfloat16, torch.float16
+
+
+def _random_case(rng):
+    D = rng.choice([32, 64, 128])
+    dtype = rng.choice([BF16, BF16, FP16])
+    Hkv = rng.choice([1, 2, 3])
+    G = rng.choice([1, 1, 2, 4])
+    B = rng.choice([1, 2])
+    Nq = rng.randint(1, 330)
+    kind = rng.choice(["square", "square", "rect", "noncausal"])
+    kw = {}
+    if kind == "square":
+        Nk = Nq
+        kw = dict(is_causal=True)
+        if rng.random() < 0.5:
+            kw["window_size"] = rng.randint(1, Nq + 5)
+    elif kind == "rect":
+        Nk = rng.randint(1, 400)
+        k_off = rng.choice([0, rng.randint(0, 2000)])
+        kw = dict(is_causal=True, k_offset=k_off, q_offset=k_off + rng.randint(0, max(0, Nk - 1)))
+        if rng.random() < 0.5:
+            kw["window_size"] = rng.randint(1, 200)
+    else:
+        Nk = rng.randint(1, 400)
+        kw = dict(is_causal=False)
+    if rng.random() < 0.3:
+        kw["scale"] = rng.uniform(0.05, 0.5)
+    return B, Hkv * G, Hkv, Nq, Nk, D, dtype, kw
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_geometry_matches_oracle(seed):
+    rng = random.Random(1234 + seed)
+    B, Hq, Hkv, Nq, Nk, D, dtype, kw = _random_case(rng)
+    q, k, v, dO, uQ = O.seeded_inputs(seed, (B, Hq, Nq, D), (B, Hkv, Nk, D), dtype, n_extra_q=2)
+    uK, uV = O.seeded_inputs(seed + 500, (B, Hq, Nq, D), (B, Hkv, Nk, D), dtype)[1:]
+    causal = kw.get("is_causal", False)
+    geom = dict(is_causal=causal, window_size=kw.get("window_size", 0),
+                q_offset=O.infer_q_offset(Nq, Nk, kw.get("q_offset"), kw.get("k_offset", 0), causal),
+                k_offset=kw.get("k_offset", 0), scale=kw.get("scale"))
+    ref = O.bob_closed_form(q, k, v, dO, uQ, uK, uV, **geom)
+    c = lambda t: t.cuda()
+    out, lse = ops.attention_forward(c(q), c(k), c(v), **geom)
+    dQ, dK, dV, delta, pk = ops.attention_first_backward(c(q), c(k), c(v), out, lse, c(dO), **geom)
+    Qb, Kb, Vb, dOb = ops.attention_second_backward(c(q), c(k), c(v), out, lse, delta, pk, c(dO), dQ, c(uQ), c(uK),
+                                                    c(uV), **geom)
+    got = dict(out=out, dQ=dQ, dK=dK, dV=dV, Qbar=Qb, Kbar=Kb, Vbar=Vb, dObar=dOb)
+    l2_bar = 8e-3 if dtype == BF16 else 1.5e-3
+    for n in O.OUTPUT_NAMES:
+        r = getattr(ref, n)
+        g = got[n]
+        assert torch.isfinite(g.float()).all(), (n, geom)
+        scale = r.abs().max().item()
+        if scale == 0:
+            assert g.float().abs().max().item() <= 0.08, (n, geom)
+            continue
+        m = O.error_metrics(g, r)
+        # tiny tensors (a handful of elements) have noisy relative norms: bound the absolute error too
+        assert m["l2_rel"] <= l2_bar or m["max_abs"] <= 0.02 * max(1.0, scale), (n, m, geom, (B, Hq, Hkv, Nq, Nk, D))
+
+
+def test_flash_attn_layout_adapter_reads_bnhd_storage_in_place():
+    B, N, Hq, Hkv, D = 2, 200, 4, 2, 64
+    g = torch.Generator().manual_seed(5)
+    r = lambda *s: torch.randn(*s, generator=g).to(BF16)
+    q, k, v = r(B, N, Hq, D), r(B, N, Hkv, D), r(B, N, Hkv, D)
+    out = adapters.flash_attn_layout(q.cuda(), k.cuda(), v.cuda(), causal=True)
+    assert out.shape == (B, N, Hq, D)
+    ref = O.attention_dense(q.transpose(1, 2).double(), k.transpose(1, 2).double(), v.transpose(1, 2).double(),
+                            is_causal=True).transpose(1, 2)
+    assert O.error_metrics(out, ref)["l2_rel"] < 6e-3
+    win = adapters.flash_attn_layout(q[:, :, :2].cuda(), k[:, :, :2].cuda(), v[:, :, :2].cuda(), causal=True,
+                                     window_size=(31, 0))
+    ref = O.attention_dense(q[:, :, :2].transpose(1, 2).double(), k[:, :, :2].transpose(1, 2).double(),
+                            v[:, :, :2].transpose(1, 2).double(), is_causal=True, window_size=32).transpose(1, 2)
+    assert O.error_metrics(win, ref)["l2_rel"] < 6e-3
+
+
+class _Block(torch.nn.Module):
+    def __init__(self, dim, heads, kv_heads, attend):
+        super().__init__()
+        self.h, self.hk, self.d = heads, kv_heads, dim // heads
+        self.wq = torch.nn.Linear(dim, heads * self.d, bias=False)
+        self.wk = torch.nn.Linear(dim, kv_heads * self.d, bias=False)
+        self.wv = torch.nn.Linear(dim, kv_heads * self.d, bias=False)
+        self.wo = torch.nn.Linear(heads * self.d, dim, bias=False)
+        self.attend = attend
+
+    def forward(self, x):
+        B, N, _ = x.shape
+        q = self.wq(x).view(B, N, self.h, self.d).transpose(1, 2)
+        k = self.wk(x).view(B, N, self.hk, self.d).transpose(1, 2)
+        v = self.wv(x).view(B, N, self.hk, self.d).transpose(1, 2)
+        o = self.attend(q, k, v)
+        return x + self.wo(o.transpose(1, 2).reshape(B, N, self.h * self.d))
+
+
+def test_hessian_vector_product_over_parameters_of_an_attention_block():
+    """Hv = d/dtheta <grad L(theta), v>: the second differentiation runs through the second backward
+    (grouped heads, strided q/k/v views) and the re-entered first backward."""
+    torch.manual_seed(0)
+    dim, heads, kv_heads, B, N = 256, 4, 2, 2, 160
+    ref_block = _Block(dim, heads, kv_heads, lambda q, k, v: O.attention_dense(q, k, v, is_causal=True)).double()
+    gpu_block = _Block(dim, heads, kv_heads, lambda q, k, v: bob.sdpa_bob(q, k, v, is_causal=True)).cuda().to(BF16)
+    with torch.no_grad():
+        for pr, pg in zip(ref_block.parameters(), gpu_block.parameters()):
+            pr.copy_(pr.to(BF16).double())
+            pg.copy_(pr.to(BF16))
+    x = torch.randn(B, N, dim).to(BF16)
+    vecs = [torch.randn_like(p).to(BF16) for p in ref_block.parameters()]
+
+    def hvp(block, x, vecs):
+        params = list(block.parameters())
+        loss = block(x).float().square().mean() if x.is_cuda else block(x).square().mean()
+        grads = torch.autograd.grad(loss, params, create_graph=True)
+        inner = sum((g.float() * v.float()).sum() if x.is_cuda else (g * v).sum() for g, v in zip(grads, vecs))
+        return torch.autograd.grad(inner, params)
+
+    want = hvp(ref_block, x.double(), [v.double() for v in vecs])
+    got = hvp(gpu_block, x.cuda(), [v.cuda() for v in vecs])
+    for w, g in zip(want, got):
+        m = O.error_metrics(g, w)
+        assert m["l2_rel"] < 3e-2, m
