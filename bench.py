@@ -407,7 +407,7 @@ def main():
                 "steps": e2e_steps, "ms_per_step": e2e_ms.item() / e2e_steps,
                 "how": "pinned host -> device -> bob_sm100_bwd2 -> pinned host every step; steps pipelined "
                        "over copy-in / compute / copy-out streams; inputs per step exceed L2"},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": lib.bob_sm100_kernel_launches(_lib.STAGE_BWD2, ctypes.byref(g)) * args.steps,
         "clocks": clocks,
         "wall_s_timed_region": wall,
         "chain": chain,

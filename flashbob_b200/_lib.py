@@ -42,6 +42,7 @@ SYMBOLS = {
     "bob_sm100_version": (ctypes.c_int, []),
     "bob_sm100_error_string": (ctypes.c_char_p, [ctypes.c_int]),
     "bob_sm100_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.POINTER(Geom)]),
+    "bob_sm100_kernel_launches": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(Geom)]),
     "bob_sm100_read_status": (ctypes.c_int, [_vp, _vp]),
     "bob_sm100_fwd": (ctypes.c_int, [ctypes.POINTER(Geom)] + [_vp] * 7),
     "bob_sm100_bwd1": (ctypes.c_int, [ctypes.POINTER(Geom)] + [_vp] * 13),

@@ -195,6 +195,11 @@ extern "C" size_t bob_sm100_workspace_bytes(int stage, const bob_sm100_geom* g) 
     return bytes;
 }
 
+extern "C" int bob_sm100_kernel_launches(int stage, const bob_sm100_geom* g) {
+    (void)g;
+    return stage == BOB_SM100_STAGE_FWD ? 1 : 2;    // one sweep, or a row-owned and a column-owned sweep
+}
+
 extern "C" int bob_sm100_read_status(const void* workspace, void* stream) {
     if (!workspace) return kErrNull;
     int v = 0;

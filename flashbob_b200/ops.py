@@ -21,8 +21,6 @@ from . import _lib
 
 _CHECK_STATUS = os.environ.get("BOB_SM100_CHECK_STATUS", "0") not in ("", "0")
 
-# number of kernels each stage launches (for launch accounting in benchmarks)
-KERNELS_PER_STAGE = {"fwd": 1, "bwd1": 2, "bwd2": 2}
 
 
 def _tma_ready(t: torch.Tensor) -> torch.Tensor:

@@ -82,6 +82,9 @@ const char* bob_sm100_error_string(int code);
 /* Scratch bytes a stage needs for this geometry (includes the 256-byte status block). */
 size_t bob_sm100_workspace_bytes(int stage, const bob_sm100_geom* geom);
 
+/* Number of kernels a stage launches for this geometry (for launch accounting). */
+int bob_sm100_kernel_launches(int stage, const bob_sm100_geom* geom);
+
 /* Waits for `stream`, then returns the status word of `workspace` (0 = every wait completed). */
 int bob_sm100_read_status(const void* workspace, void* stream);
 
