@@ -133,7 +133,7 @@ struct SweepConfig {
     static constexpr int OFF_STAT = OFF_OTH + NSTAGE * OTH_STAGE_BYTES;         // [NSTAGE][4][TN] floats
     static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [2][NG * NSPLIT][128] floats
     static constexpr int OFF_BAR = OFF_RED + 2 * NG * NSPLIT * 128 * 4;
-    static constexpr int NBARS = 1 + 3 * NSTAGE + 2 + 5 * NG;
+    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag
     static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;                     // + alignment slack
     static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
@@ -206,7 +206,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     auto bar_stat = [&](int s) { return bar0 + 8u * (1 + 2 * NSTAGE + s); };     // per stage: row statistics staged
     const uint32_t bar_done = bar0 + 8u * (1 + 3 * NSTAGE);
     const uint32_t bar_pw_all = bar_done + 8;                                  // all pointwise threads
-    const uint32_t bar_grp0 = bar_done + 16;                                   // five barriers per group:
+    const uint32_t bar_out_free = bar_done + 16;                               // output accumulators read out
+    const uint32_t bar_grp0 = bar_done + 24;                                   // five barriers per group:
     auto bar_sc_full = [&](int g) { return bar_grp0 + 40u * g; };             //   scores ready
     auto bar_sc_empty = [&](int g) { return bar_grp0 + 40u * g + 8; };        //   scores read
     auto bar_op_full = [&](int g) { return bar_grp0 + 40u * g + 16; };        //   operands written
@@ -217,42 +218,59 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
-    // ---- which tile this CTA owns, and the range of tiles it sweeps --------------------------
-    // The grid is one-dimensional and ordered longest-sweep-first: all heads' heaviest tile, then
-    // all heads' second heaviest, ... so the tail of the launch consists of short sweeps.
+    // ---- work items ----------------------------------------------------------------------------
+    // One item = one own tile of one head of one batch element, swept over the other side.  Items
+    // are numbered longest-sweep-first (all heads' heaviest tile, then all heads' second heaviest,
+    // ...).  The kernel is persistent: CTA c takes items c, c + gridDim.x, ..., keeps its tensor
+    // memory and barriers, and lets the TMA and MMA warps start an item while the pointwise threads
+    // still write out the previous one.
     const int n_own = COL ? p.Nk : p.Nq;
     const int n_oth = COL ? p.Nq : p.Nk;
     const int n_own_tiles = (n_own + 127) / 128;
     const int grid_heads = COL ? p.Hkv : p.Hq;
     const int per_rank = grid_heads * p.B;
-    const int tile_rank = (int)blockIdx.x / per_rank;
-    const int rem = (int)blockIdx.x % per_rank;
-    const int head = rem % grid_heads;           // query head (row-owned) or KV head (column-owned)
-    const int batch = rem / grid_heads;
-    // causal: row-owned sweeps grow with the row index, column-owned ones shrink with the column
-    const int own_tile = (!COL && p.is_causal) ? (n_own_tiles - 1 - tile_rank) : tile_rank;
-    const int own0 = own_tile * 128;
-    const int kv_head = COL ? head : head / p.G;
+    const int n_items = n_own_tiles * per_rank;
     const int n_outer = (MODE == kFwd) ? 2 : (COL ? p.G : 1);
     const int doff = p.delta_off;                // q_offset - k_offset, clamped to +-2^30 by the host
-
-    int lo = 0, hi = n_oth;                      // other-side positions [lo, hi) that can be unmasked
-    {
-        const int own_last = min(own0 + 127, n_own - 1);
+    struct Item { int own0, head, batch, kv_head, t_lo, t_hi, T, total; };
+    auto decode = [&](int item) {
+        Item w;
+        const int tile_rank = item / per_rank;
+        const int rem = item % per_rank;
+        w.head = rem % grid_heads;               // query head (row-owned) or KV head (column-owned)
+        w.batch = rem / grid_heads;
+        // causal: row-owned sweeps grow with the row index, column-owned ones shrink with the column
+        const int own_tile = (!COL && p.is_causal) ? (n_own_tiles - 1 - tile_rank) : tile_rank;
+        w.own0 = own_tile * 128;
+        w.kv_head = COL ? w.head : w.head / p.G;
+        int lo = 0, hi = n_oth;                  // other-side positions [lo, hi) that can be unmasked
+        const int own_last = min(w.own0 + 127, n_own - 1);
         if (p.is_causal) {
             if (!COL) {
                 hi = (int)min((long long)n_oth, (long long)own_last + doff + 1);
-                if (p.window > 0) lo = (int)max(0LL, (long long)own0 + doff - p.window + 1);
+                if (p.window > 0) lo = (int)max(0LL, (long long)w.own0 + doff - p.window + 1);
             } else {
-                lo = (int)max(0LL, (long long)own0 - doff);
+                lo = (int)max(0LL, (long long)w.own0 - doff);
                 if (p.window > 0) hi = (int)min((long long)n_oth, (long long)own_last - doff + p.window);
             }
         }
-    }
-    const int t_lo = (hi > lo) ? lo / TN : 0;
-    const int t_hi = (hi > lo) ? (hi + TN - 1) / TN : 0;
-    const int T = t_hi - t_lo;
-    const int total = T * n_outer;
+        w.t_lo = (hi > lo) ? lo / TN : 0;
+        w.t_hi = (hi > lo) ? (hi + TN - 1) / TN : 0;
+        w.T = w.t_hi - w.t_lo;
+        w.total = w.T * n_outer;
+        return w;
+    };
+    // Round r of this CTA: rounds alternate direction over the longest-first item list, so that a CTA
+    // that got a long item in one round gets a short one in the next.  -1: no item in this round.
+    const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    auto item_of = [&](int r) {
+        const int i = r * (int)gridDim.x + ((r & 1) ? ((int)gridDim.x - 1 - (int)blockIdx.x) : (int)blockIdx.x);
+        return i < n_items ? i : -1;
+    };
+#define BOB_ITEM_LOCALS(w)                                                                         \
+    const int own0 = (w).own0, head = (w).head, batch = (w).batch, kv_head = (w).kv_head;         \
+    const int t_lo = (w).t_lo, t_hi = (w).t_hi, T = (w).T, total = (w).total;                      \
+    (void)own0; (void)head; (void)batch; (void)kv_head; (void)t_lo; (void)t_hi; (void)T; (void)total;
 
     // ---- set-up ------------------------------------------------------------------------------
     if (tid == 0) {
@@ -267,6 +285,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
         mbar_init(bar_done, 1);
         mbar_init(bar_pw_all, NPW / 32);
+        mbar_init(bar_out_free, NPW / 32);
         misc[1] = 0;
         mbar_fence_init();
     }
@@ -301,78 +320,95 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         // Lane 0 issues the TMA copies.  In column-owned modes all 32 lanes also stage the swept
         // tile's per-query statistics, negated, into the stage's statistics buffer:
         // [-lse*log2e | -delta | -alpha | -ecirc], TN floats each.
-        if (lane == 0) {
-            uint32_t own_bytes = 0;
-            #pragma unroll
-            for (int i = 0; i < MT::NOWN; ++i)
-                if (has_tensor(own_tensor<MODE>(i))) own_bytes += CFG::OWN_TILE_BYTES;
-            mbar_arrive_expect_tx(bar_own, own_bytes);
-            #pragma unroll
-            for (int i = 0; i < MT::NOWN; ++i) {
-                const int t = own_tensor<MODE>(i);
-                if (!has_tensor(t)) continue;
-                #pragma unroll
-                for (int ks = 0; ks < KSUB; ++ks)
-                    tma_load_4d(sbase + CFG::OFF_OWN + i * CFG::OWN_TILE_BYTES + ks * (128 * 128),
-                                &p.map[t], bar_own, ks * 64, own0, head, batch);
-            }
-        }
-        int issued = 0;
-        int s = 0, round = 0;                    // pipeline stage of iteration `it`, and it / NSTAGE
-        int tile = t_lo, outer = 0;              // swept tile of iteration `it`, and it / T
-        for (int it = 0; it < total; ++it) {
-            bool go = true;
-            if (it >= NSTAGE) go = mbar_wait(bar_empty(s), (round - 1) & 1);
-            go = __all_sync(0xffffffffu, go);
-            if (!go) { if (lane == 0) give_up(kStatusTimeoutLoad); break; }
-            const int oth_head = COL ? (head * p.G + outer) : kv_head;
-            if (lane == 0) {
-                uint32_t bytes = 0;
-                #pragma unroll
-                for (int i = 0; i < MT::NOTH; ++i) {
-                    if (MODE == kFwd && outer == 0 && i == 1) continue;     // the statistics sweep needs K only
-                    if (has_tensor(other_tensor<MODE>(i))) bytes += KSUB * CFG::OTH_SUB_BYTES;
+        int cnt = 0;                             // swept tiles issued so far, over all items
+        int s = 0, round = 0;                    // pipeline stage of tile `cnt`, and cnt / NSTAGE
+        int n_live = 0;                          // items with at least one tile started so far
+        bool alive = true;
+        for (int r = 0; alive && r < n_rounds; ++r) {
+            const int item = item_of(r);
+            if (item < 0) continue;
+            const Item w = decode(item);
+            BOB_ITEM_LOCALS(w)
+            if (total == 0) continue;
+            if (n_live > 0) {
+                // the previous item's last products have finished reading its own tiles
+                if (!__all_sync(0xffffffffu, mbar_wait(bar_done, (n_live - 1) & 1))) {
+                    if (lane == 0) give_up(kStatusTimeoutLoad);
+                    break;
                 }
-                mbar_arrive_expect_tx(bar_full(s), bytes);
+            }
+            if (lane == 0) {
+                uint32_t own_bytes = 0;
                 #pragma unroll
-                for (int i = 0; i < MT::NOTH; ++i) {
-                    const int t = other_tensor<MODE>(i);
-                    if (MODE == kFwd && outer == 0 && i == 1) continue;
+                for (int i = 0; i < MT::NOWN; ++i)
+                    if (has_tensor(own_tensor<MODE>(i))) own_bytes += CFG::OWN_TILE_BYTES;
+                mbar_arrive_expect_tx(bar_own, own_bytes);
+                #pragma unroll
+                for (int i = 0; i < MT::NOWN; ++i) {
+                    const int t = own_tensor<MODE>(i);
                     if (!has_tensor(t)) continue;
                     #pragma unroll
                     for (int ks = 0; ks < KSUB; ++ks)
-                        tma_load_4d(oth_addr(s, ks, i), &p.map[t], bar_full(s), ks * 64, tile * TN, oth_head, batch);
+                        tma_load_4d(sbase + CFG::OFF_OWN + i * CFG::OWN_TILE_BYTES + ks * (128 * 128),
+                                    &p.map[t], bar_own, ks * 64, own0, head, batch);
                 }
             }
-            if constexpr (COL) {
-                float* sb = stat_buf + s * 4 * TN;
-                #pragma unroll
-                for (int r = lane; r < TN; r += 32) {
-                    const int i = tile * TN + r;
-                    float l2 = 0.f, d = 0.f, al = 0.f, ec = 0.f;
-                    if (i < p.Nq) {
-                        const long long off = ((long long)batch * p.Hq + oth_head) * p.Nq + i;
-                        l2 = p.lse[off] * kLog2e;
-                        d = p.delta[off];
-                        if constexpr (MODE == kBwd2Col) { al = p.alpha[off]; ec = p.ecirc[off]; }
+            ++n_live;
+            int tile = t_lo, outer = 0;              // swept tile of iteration `it`, and it / T
+            for (int it = 0; it < total; ++it) {
+                bool go = true;
+                if (cnt >= NSTAGE) go = mbar_wait(bar_empty(s), (round - 1) & 1);
+                go = __all_sync(0xffffffffu, go);
+                if (!go) { if (lane == 0) give_up(kStatusTimeoutLoad); alive = false; break; }
+                const int oth_head = COL ? (head * p.G + outer) : kv_head;
+                if (lane == 0) {
+                    uint32_t bytes = 0;
+                    #pragma unroll
+                    for (int i = 0; i < MT::NOTH; ++i) {
+                        if (MODE == kFwd && outer == 0 && i == 1) continue;     // the statistics sweep needs K only
+                        if (has_tensor(other_tensor<MODE>(i))) bytes += KSUB * CFG::OTH_SUB_BYTES;
                     }
-                    sb[r] = -l2; sb[TN + r] = -d; sb[2 * TN + r] = -al; sb[3 * TN + r] = -ec;
+                    mbar_arrive_expect_tx(bar_full(s), bytes);
+                    #pragma unroll
+                    for (int i = 0; i < MT::NOTH; ++i) {
+                        const int t = other_tensor<MODE>(i);
+                        if (MODE == kFwd && outer == 0 && i == 1) continue;
+                        if (!has_tensor(t)) continue;
+                        #pragma unroll
+                        for (int ks = 0; ks < KSUB; ++ks)
+                            tma_load_4d(oth_addr(s, ks, i), &p.map[t], bar_full(s), ks * 64, tile * TN, oth_head, batch);
+                    }
                 }
-                mbar_arrive(bar_stat(s));
+                if constexpr (COL) {
+                    float* sb = stat_buf + s * 4 * TN;
+                    #pragma unroll
+                    for (int r = lane; r < TN; r += 32) {
+                        const int i = tile * TN + r;
+                        float l2 = 0.f, d = 0.f, al = 0.f, ec = 0.f;
+                        if (i < p.Nq) {
+                            const long long off = ((long long)batch * p.Hq + oth_head) * p.Nq + i;
+                            l2 = p.lse[off] * kLog2e;
+                            d = p.delta[off];
+                            if constexpr (MODE == kBwd2Col) { al = p.alpha[off]; ec = p.ecirc[off]; }
+                        }
+                        sb[r] = -l2; sb[TN + r] = -d; sb[2 * TN + r] = -al; sb[3 * TN + r] = -ec;
+                    }
+                    mbar_arrive(bar_stat(s));
+                }
+                ++cnt;
+                if (++s == NSTAGE) { s = 0; ++round; }
+                if (++tile == t_hi) { tile = t_lo; ++outer; }
             }
-            ++issued;
-            if (++s == NSTAGE) { s = 0; ++round; }
-            if (++tile == t_hi) { tile = t_lo; ++outer; }
         }
         // Do not leave while copies into this CTA's shared memory may still be in flight.
         if (lane == 0) {
-            for (int k = max(0, issued - NSTAGE); k < issued; ++k)
+            for (int k = max(0, cnt - NSTAGE); k < cnt; ++k)
                 mbar_wait(bar_full(k % NSTAGE), (k / NSTAGE) & 1);
-            mbar_wait(bar_own, 0);
+            if (n_live > 0) mbar_wait(bar_own, (n_live - 1) & 1);
         }
     } else if (warp == NPW / 32) {
         // =========================== MMA issuer ===============================================
-        if (total > 0) {
+        {
             constexpr uint32_t fmt = BF16 ? kFmtBF16 : kFmtF16;
 
             // Descriptor low words: (shared-memory address >> 4) | 0x10000 (leading byte offset 16).
@@ -416,11 +452,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             using NS2 = IntTag<2>;
 
             BOB_PH_DECL
-            // scores of iteration `it` (group it % NG, that group's tile number it / NG), whose swept
-            // tiles sit in pipeline stage `stage` (use number `round`)
-            auto issue_scores = [&](int it, int stage, int round) -> bool {
+            // scores of the tile with running number `gcnt` (counted over all items of this CTA; group
+            // gcnt % NG, that group's tile number gcnt / NG), whose swept tiles sit in pipeline stage
+            // `stage` (use number `round`)
+            auto issue_scores = [&](int gcnt, int stage, int round) -> bool {
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
-                const int g = it % NG, j = it / NG;
+                const int g = gcnt % NG, j = gcnt / NG;
                 const uint32_t sc = tmem + g * CFG::SC_COLS;
                 BOB_PH(7)
                 if (!__all_sync(0xffffffffu, mbar_wait(bar_full(stage), round & 1))) { give_up(kStatusTimeoutMma); return false; }
@@ -453,21 +490,38 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 return true;
             };
 
-            bool ok = __all_sync(0xffffffffu, mbar_wait(bar_own, 0));
+            int cnt = 0;                              // swept tiles issued so far, over all items
+            int stage = 0, round = 0;                 // pipeline stage of tile `cnt`, and cnt / NSTAGE
+            int n_out0 = 0, n_out1 = 0;               // output rounds issued so far, per pointwise group
+            int n_live = 0;                           // items with at least one tile finished so far
+            bool ok = true;
+            for (int r = 0; ok && r < n_rounds; ++r) {
+            const int item = item_of(r);
+            if (item < 0) continue;
+            const Item w = decode(item);
+            BOB_ITEM_LOCALS(w)
+            if (total == 0) continue;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
             if (!ok) give_up(kStatusTimeoutMma);
-            ok = ok && issue_scores(0, 0, 0);
-            int n_out = 0;      // output rounds issued so far
-            int stage = 0;                            // stage of iteration `it`
-            int nstage = (NSTAGE > 1) ? 1 : 0, nround = (NSTAGE > 1) ? 0 : 1;   // stage / use number of iteration it + 1
+            ok = ok && issue_scores(cnt, stage, round);
+            int n_out = 0;                            // output rounds of this item
             for (int it = 0; ok && it < total; ++it) {
-                if (it + 1 < total && !issue_scores(it + 1, nstage, nround)) break;
+                int nstage = stage + 1, nround = round;
+                if (nstage == NSTAGE) { nstage = 0; ++nround; }
+                if (it + 1 < total && !issue_scores(cnt + it + 1, nstage, nround)) { ok = false; break; }
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
                 const bool has_out = (MODE != kFwd) || it >= T;
                 if (has_out) {
-                    const int g = it % NG;
+                    const int g = (cnt + it) % NG;
                     const uint32_t ob = tmem_oper + g * CFG::OPER_COLS;
+                    int& n_out_g = (g == 0) ? n_out0 : n_out1;
                     BOB_PH(7)
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar_op_full(g), (n_out / NG) & 1))) { give_up(kStatusTimeoutMma); break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar_op_full(g), n_out_g & 1))) { give_up(kStatusTimeoutMma); ok = false; break; }
+                    // the first products of an item overwrite the output accumulators: the pointwise
+                    // threads must have read out the previous item's
+                    if (n_out == 0 && n_live > 0 &&
+                        !__all_sync(0xffffffffu, mbar_wait(bar_out_free, (n_live - 1) & 1))) { give_up(kStatusTimeoutMma); ok = false; break; }
+                    ++n_out_g;
                     BOB_PH(3)
                     tc_fence_after_sync();
                     const bool acc = n_out > 0;
@@ -495,11 +549,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     ++n_out;
                 }
                 if (elect_one()) umma_commit(bar_empty(stage));
-                stage = nstage;
-                if (++nstage == NSTAGE) { nstage = 0; ++nround; }
+                stage = nstage; round = nround;
                 BOB_PH(4)
             }
+            cnt += total;
             if (elect_one()) umma_commit(bar_done);
+            ++n_live;
+            }   // items
             BOB_PH_FLUSH(8, lane == 0)
         }
     } else {
@@ -509,12 +565,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         const int row = gtid & 127;              // own row inside the tile == tensor-memory lane
         const int sp = gtid >> 7;                // which 16-column slice of every score tile
         const int col0 = sp * CW;                // my first column inside a swept tile
-        const int own_idx = own0 + row;
-        const bool own_ok = own_idx < n_own;
         const uint32_t tlane = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);   // my lane, column 0
         const uint32_t tsc = tlane + grp * CFG::SC_COLS;                                  // my group's scores
         const float c_exp = p.scale * kLog2e;
-        const long long row_stat = ((long long)batch * p.Hq + head) * p.Nq + own_idx;   // row-owned only
 
         // where my 16 columns (8 packed words) of operand k go in tensor memory
         const uint32_t op_taddr = tlane + NG * CFG::SC_COLS + grp * CFG::OPER_COLS + (col0 >> 1);
@@ -537,6 +590,21 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             return r;
         };
         bool ok = true;
+        uint32_t pw_all_phase = 0;               // phase of the all-groups barrier
+        int cnt = 0;                             // swept tiles seen so far, over all items
+        int stage = 0, round = 0;                // pipeline stage of tile `cnt`, and cnt / NSTAGE
+        int n_op = 0;                            // operand rounds my group has written so far
+        int n_live = 0;                          // items with at least one tile finished so far
+        BOB_PH_DECL
+
+        for (int r = 0; ok && r < n_rounds; ++r) {
+            const int item = item_of(r);
+            if (item < 0) continue;
+        const Item w = decode(item);
+        BOB_ITEM_LOCALS(w)
+        const int own_idx = own0 + row;
+        const bool own_ok = own_idx < n_own;
+        const long long row_stat = ((long long)batch * p.Hq + head) * p.Nq + own_idx;   // row-owned only
 
         // per-row state (row-owned modes): -lse*log2e and -delta of my row
         float nL2 = 0.f, ndlt = 0.f;
@@ -576,12 +644,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             if (own_ok) { nL2 = -p.lse[row_stat] * kLog2e; ndlt = -p.delta[row_stat]; }
         }
 
-        int n_op = 0;                            // operand rounds written so far
         bool fwd_combined = false;               // forward: first-sweep statistics already combined
-        BOB_PH_DECL
 
         // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
-        auto tile_body = [&](auto full_tag, int it, int tile, int outer, int stage, int round) -> bool {
+        auto tile_body = [&](auto full_tag, int it, int gcnt, int tile, int outer, int stage, int round) -> bool {
             constexpr bool FULL = decltype(full_tag)::value;
             const int oth0 = tile * TN;
 
@@ -596,7 +662,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     fwd_combined = true;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_pw_all);
-                    if (!pw_wait(bar_pw_all, 0)) return false;
+                    if (!pw_wait(bar_pw_all, pw_all_phase)) return false;
                     float m = -1e30f;
                     #pragma unroll
                     for (int k = 0; k < NPART; ++k) m = fmaxf(m, red_buf[k * 128 + row]);
@@ -615,7 +681,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 // the swept tile's row statistics were staged by the producer warp
                 if (!pw_wait(bar_stat(stage), round & 1)) return false;
             }
-            if (!pw_wait(bar_sc_full(grp), (it / NG) & 1)) return false;
+            if (!pw_wait(bar_sc_full(grp), (gcnt / NG) & 1)) return false;
             BOB_PH(0)
             tc_fence_after_sync();
 
@@ -817,28 +883,28 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             return true;
         };
 
-        int tile = t_lo, outer = 0, stage = 0, round = 0;
-        auto advance = [&]() {
-            if (++tile == t_hi) { tile = t_lo; ++outer; }
-            if (++stage == NSTAGE) { stage = 0; ++round; }
-        };
-        for (int k = 0; k < grp; ++k) advance();
-        for (int it = grp; ok && it < total; it += NG) {
-            // is the whole 128 x TN tile pair unmasked and inside both tensors?  (uniform per CTA)
-            const int oth0 = tile * TN;
-            bool full = (own0 + 127 < n_own) && (oth0 + TN <= n_oth);
-            if (p.is_causal) {
-                const int dmin = COL ? (oth0 + doff - (own0 + 127)) : (own0 + doff - (oth0 + TN - 1));
-                const int dmax = COL ? (oth0 + TN - 1 + doff - own0) : (own0 + 127 + doff - oth0);
-                full = full && dmin >= 0 && (p.window == 0 || dmax < p.window);
+        BOB_PH(6)
+        {
+            int tile = t_lo, outer = 0;
+            for (int it = 0; ok && it < total; ++it) {
+                if ((cnt + it) % NG == grp) {            // my group's turn
+                    // is the whole 128 x TN tile pair unmasked and inside both tensors?  (uniform per CTA)
+                    const int oth0 = tile * TN;
+                    bool full = (own0 + 127 < n_own) && (oth0 + TN <= n_oth);
+                    if (p.is_causal) {
+                        const int dmin = COL ? (oth0 + doff - (own0 + 127)) : (own0 + doff - (oth0 + TN - 1));
+                        const int dmax = COL ? (oth0 + TN - 1 + doff - own0) : (own0 + 127 + doff - oth0);
+                        full = full && dmin >= 0 && (p.window == 0 || dmax < p.window);
+                    }
+                    ok = full ? tile_body(BoolTag<true>{}, it, cnt + it, tile, outer, stage, round)
+                              : tile_body(BoolTag<false>{}, it, cnt + it, tile, outer, stage, round);
+                }
+                if (++tile == t_hi) { tile = t_lo; ++outer; }
+                if (++stage == NSTAGE) { stage = 0; ++round; }
             }
-            ok = full ? tile_body(BoolTag<true>{}, it, tile, outer, stage, round)
-                      : tile_body(BoolTag<false>{}, it, tile, outer, stage, round);
-            #pragma unroll
-            for (int k = 0; k < NG; ++k) advance();
+            cnt += total;
         }
 
-        BOB_PH_FLUSH(0, tid == 0)
         // ---- epilogue ------------------------------------------------------------------------
         if constexpr (MODE == kFwd) {
             if (total == 0 && grp == 0 && sp == 0 && own_ok) p.lse[row_stat] = -INFINITY;
@@ -849,6 +915,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pw_all);
             }
+            if (total > 0) pw_all_phase ^= 1u;       // one use of the all-groups barrier per item
         }
         float alpha = 0.f, ecirc = 0.f;
         ok = __all_sync(0xffffffffu, ok);
@@ -859,32 +926,64 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             if (ok) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pw_all);
-                ok = pw_wait(bar_pw_all, 0);
+                ok = pw_wait(bar_pw_all, pw_all_phase);
+                pw_all_phase ^= 1u;
             }
             #pragma unroll
             for (int k = 0; k < NPART; ++k) { alpha += red_buf[k * 128 + row]; ecirc += red_buf[(NPART + k) * 128 + row]; }
             if (ok && grp == 0 && sp == 0 && own_ok) { p.alpha[row_stat] = alpha; p.ecirc[row_stat] = ecirc; }
         }
-        if (ok && total > 0) ok = pw_wait(bar_done, 0);
+        if (ok && total > 0) ok = pw_wait(bar_done, n_live & 1);
         tc_fence_after_sync();
         if (ok) {
             constexpr int DC = DPAD / (NSPLIT * NG);    // output columns per pointwise thread
+            constexpr int NCH = DC / 16;
             const int res_heads = COL ? p.Hkv : p.Hq;
             const long long res_off = (((long long)batch * res_heads + head) * n_own + own_idx) * p.D;
-            #pragma unroll 1
-            for (int c = 0; c < DC; c += 16) {
-                const int col = (grp * NSPLIT + sp) * DC + c;
-                if (col >= p.D) break;
-                float a0[16], a1[16];
-                if (total > 0) {
-                    tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 0 * DPAD + col, a0);
-                    if constexpr (MT::NOUT > 1) tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 1 * DPAD + col, a1);
-                    tmem_wait_ld();
+            // All of my accumulator columns come out of tensor memory first (warp-wide loads), so that
+            // the MMA warp may start overwriting them for the next item while I combine and store.
+            // (With more than two 16-column chunks per thread that would cost too many registers: then
+            // the chunks are taken one at a time and the accumulators are released after the last.)
+            constexpr bool EARLY = NCH <= 2;
+            float acc0[EARLY ? NCH : 1][16], acc1[EARLY ? NCH : 1][16];
+            #pragma unroll
+            for (int ch = 0; ch < (EARLY ? NCH : 0); ++ch) {
+                const int col = (grp * NSPLIT + sp) * DC + 16 * ch;
+                if (total > 0 && col < p.D) {
+                    tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 0 * DPAD + col, acc0[ch]);
+                    if constexpr (MT::NOUT > 1) tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 1 * DPAD + col, acc1[ch]);
                 } else {
                     #pragma unroll
-                    for (int i = 0; i < 16; ++i) { a0[i] = 0.f; a1[i] = 0.f; }
+                    for (int i = 0; i < 16; ++i) { acc0[ch][i] = 0.f; acc1[ch][i] = 0.f; }
                 }
-                if (!own_ok) continue;          // tensor-memory loads above are warp-wide; stores are per row
+            }
+            auto release_outputs = [&]() {
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_out_free);
+            };
+            bool released = false;
+            if (EARLY && total > 0) { release_outputs(); released = true; }
+            #pragma unroll
+            for (int c = 0; c < DC; c += 16) {
+                const int col = (grp * NSPLIT + sp) * DC + c;
+                const bool last = (c + 16 >= DC) || (col + 16 >= p.D);
+                if (col >= p.D) break;
+                float late0[16], late1[16];
+                if constexpr (!EARLY) {
+                    if (total > 0) {
+                        tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 0 * DPAD + col, late0);
+                        if constexpr (MT::NOUT > 1) tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 1 * DPAD + col, late1);
+                        if (last) { release_outputs(); released = true; } else tmem_wait_ld();
+                    } else {
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) { late0[i] = 0.f; late1[i] = 0.f; }
+                    }
+                }
+                float* a0 = EARLY ? acc0[EARLY ? c / 16 : 0] : late0;
+                float* a1 = EARLY ? acc1[EARLY ? c / 16 : 0] : late1;
+                if (!own_ok) continue;          // stores are per row
                 if constexpr (MODE == kFwd) {
                     store16_from_float<BF16>(p.res0, res_off + col, a0);
                 } else if constexpr (MODE == kBwd1Row) {
@@ -927,8 +1026,14 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     store16_from_float<BF16>(p.res1, res_off + col, a1);
                 }
             }
+            if (total > 0 && !released) release_outputs();   // a thread with no column inside the head dim
         }
+        if (total > 0) ++n_live;
+        BOB_PH(5)
+        }   // items
+        BOB_PH_FLUSH(0, tid == 0)
     }
+#undef BOB_ITEM_LOCALS
 
     // ---- teardown --------------------------------------------------------------------------------
     tc_fence_before_sync();
