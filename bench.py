@@ -53,6 +53,13 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one second-backward launch pair, from the ncu capture
+# summarised in profiles/bwd2_kernels_gqa_s4096_d64.md: that capture ran a quarter of the c2 workload
+# (8 of 32 query heads; traffic grows with the head count), so its 51.3 MB is scaled by 4.
+TRAFFIC_BYTES = {"c2": 4 * (33_884_416 + 1_792 + 17_369_088)}
+TRAFFIC_NOTE = "ncu dram bytes of the row-owned + column-owned kernels on a quarter-size capture, x4; c2 only"
+
+
 def causal_pairs(n: int) -> int:
     return n * (n + 1) // 2
 
@@ -400,7 +407,8 @@ def main():
         "frac_of_nominal_2250": per_gpu / 2250.0,
         "roofline": {"bound": "tensor", "achieved": flops_rank / (ms_per_step * 1e-3) / 1e12, "peak": peak,
                      "unit": UNIT, "frac": flops_rank / (ms_per_step * 1e-3) / 1e12 / peak,
-                     "traffic": None, "peak_source": peak_src,
+                     "traffic": TRAFFIC_BYTES.get(args.workload), "traffic_source": TRAFFIC_NOTE,
+                     "peak_source": peak_src,
                      "kernel": "second backward = row-owned kernel + column-owned kernel",
                      "kernel_ms": kernel_ms},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -49,6 +49,7 @@ SYMBOLS = {
     "bob_sm100_bwd2": (ctypes.c_int, [ctypes.POINTER(Geom)] + [_vp] * 18),
     "bob_sm100_noalloc_max_rows": (ctypes.c_size_t, []),
     "bob_sm100_bwd2_noalloc": (ctypes.c_int, [ctypes.POINTER(Geom)] + [_vp] * 17),
+    "bob_sm100_timeout_selftest": (ctypes.c_int, [_vp, _vp]),
     "bob_sm100_selftest": (ctypes.c_int, [_vp, _vp, ctypes.c_int, _vp, _vp, _vp]),
 }
 

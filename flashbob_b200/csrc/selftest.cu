@@ -14,6 +14,8 @@
 
 namespace bob {
 
+enum : int { kSelftestTimedOut = 77 };
+
 struct SelftestMaps {
     CUtensorMap a;
     CUtensorMap b;
@@ -163,7 +165,28 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
+// A wait that nothing completes: the bounded wait must give up and report, not spin forever.
+__global__ void timeout_selftest_kernel(int* __restrict__ status) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const bool done = mbar_wait(b, 0);          // nobody arrives on this barrier
+    if (threadIdx.x == 0) atomicExch(status, done ? 0 : kSelftestTimedOut);
+}
+
 }  // namespace bob
+
+extern "C" int bob_sm100_timeout_selftest(int* status, void* stream) {
+    if (!status) return -1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess) return -3;
+    bob::timeout_selftest_kernel<<<1, 32, 0, s>>>(status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 extern "C" int bob_sm100_selftest(const void* a, const void* b, int is_bf16, float* out,
                                   int* status, void* stream) {

@@ -132,6 +132,11 @@ int bob_sm100_bwd2_noalloc(const bob_sm100_geom* geom, const void* q, const void
 int bob_sm100_selftest(const void* a, const void* b, int is_bf16, float* out, int* status,
                        void* stream);
 
+/* Failure-detection check: launches one warp that waits on a barrier nothing completes.  The
+ * library's bounded wait gives up after about half a second of SM cycles and the kernel writes 77
+ * to *status (a device int) and returns normally; the context stays usable. */
+int bob_sm100_timeout_selftest(int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

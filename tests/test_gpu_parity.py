@@ -78,6 +78,17 @@ def test_tensor_core_plumbing_known_answer():
             torch.testing.assert_close(out[i].double(), ab, rtol=1e-5, atol=1e-4)
 
 
+def test_bounded_wait_gives_up_and_reports():
+    """Failure detection without a fault: a wait that nothing completes runs out after ~0.5 s of SM
+    cycles, the kernel records a status and returns, and the context keeps working."""
+    lib = _lib.load()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.bob_sm100_timeout_selftest(st.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert st.item() == 77
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0      # context still usable
+
+
 CASES = {
     # name: (B, Hq, Hkv, Nq, Nk, D, dtype, kwargs)
     "causal64": (1, 2, 2, 64, 64, 64, BF16, dict(is_causal=True)),
