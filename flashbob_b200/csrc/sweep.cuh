@@ -644,7 +644,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             if (own_ok) { nL2 = -p.lse[row_stat] * kLog2e; ndlt = -p.delta[row_stat]; }
         }
 
-        bool fwd_combined = false;               // forward: first-sweep statistics already combined
+        bool fwd_combined = false;               // forward: first-sweep maxima already combined
+        bool lse_writer = false;                 // forward: this thread writes the row's lse
 
         // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
         auto tile_body = [&](auto full_tag, int it, int gcnt, int tile, int outer, int stage, int round) -> bool {
@@ -653,12 +654,11 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
 
             if constexpr (MODE == kFwd) {
                 if (outer == 1 && !fwd_combined) {
-                    // between the two sweeps: combine every slice's (max, sum) into the row's lse.
+                    // between the two sweeps: combine every slice's maximum into the row maximum.
                     // Each pointwise thread of the CTA arrives once: here, before its first tile of
                     // the second sweep, or after its loop if it has no such tile.
                     constexpr int NPART = NG * NSPLIT;
                     red_buf[(grp * NSPLIT + sp) * 128 + row] = run_max;
-                    red_buf[(NPART + grp * NSPLIT + sp) * 128 + row] = run_sum;
                     fwd_combined = true;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_pw_all);
@@ -666,13 +666,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     float m = -1e30f;
                     #pragma unroll
                     for (int k = 0; k < NPART; ++k) m = fmaxf(m, red_buf[k * 128 + row]);
-                    float l = 0.f;
-                    #pragma unroll
-                    for (int k = 0; k < NPART; ++k)
-                        l += red_buf[(NPART + k) * 128 + row] * fast_exp2(red_buf[k * 128 + row] - m);
-                    const float L2 = (l > 0.f) ? m + log2f(l) : INFINITY;
-                    nL2 = -L2;
-                    if (it == T && sp == 0 && own_ok) p.lse[row_stat] = (l > 0.f) ? L2 * kLn2 : -INFINITY;
+                    nL2 = -m;                            // second sweep: p = exp2(s - max), summed as it goes
+                    lse_writer = (it == T && sp == 0);   // exactly one thread per row
                 }
             }
 
@@ -715,19 +710,16 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_sc_empty(grp));
                 if (outer == 0) {
+                    // first sweep: the row maximum only (no exponentials)
                     float mx = run_max;
                     #pragma unroll
-                    for (int c = 0; c < CW; ++c) {
-                        s_[c] = (FULL || ((vmask >> c) & 1u)) ? s_[c] * c_exp : -1e30f;
-                        mx = fmaxf(mx, s_[c]);
-                    }
-                    float sum = run_sum * fast_exp2(run_max - mx);
-                    #pragma unroll
                     for (int c = 0; c < CW; ++c)
-                        sum += (FULL || ((vmask >> c) & 1u)) ? fast_exp2(s_[c] - mx) : 0.f;
-                    run_max = mx; run_sum = sum;
+                        mx = fmaxf(mx, (FULL || ((vmask >> c) & 1u)) ? s_[c] * c_exp : -1e30f);
+                    run_max = mx;
                     return true;
                 }
+                // second sweep: unnormalised probabilities relative to the row maximum; their sum
+                // normalises the output in the epilogue
                 uint32_t w0[CW / 2];
                 #pragma unroll
                 for (int c2 = 0; c2 < CW / 2; ++c2) {
@@ -737,6 +729,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         a = ((vmask >> (2 * c2)) & 1u) ? a : 0.f;
                         b = ((vmask >> (2 * c2 + 1)) & 1u) ? b : 0.f;
                     }
+                    run_sum += a + b;
                     w0[c2] = pack2<BF16>(a, b);
                 }
                 if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
@@ -909,13 +902,31 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         if constexpr (MODE == kFwd) {
             if (total == 0 && grp == 0 && sp == 0 && own_ok) p.lse[row_stat] = -INFINITY;
             if (total > 0 && !fwd_combined) {
-                constexpr int NPART = NG * NSPLIT;
                 red_buf[(grp * NSPLIT + sp) * 128 + row] = run_max;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_pw_all);
+                // a second arrival (below) must not land in this phase: wait until it has completed
+                if (ok) ok = pw_wait(bar_pw_all, pw_all_phase);
+            }
+            if (total > 0) pw_all_phase ^= 1u;       // first use of the all-groups barrier in this item
+        }
+        float fwd_inv_l = 0.f;                       // forward: 1 / (sum of the row's probabilities)
+        if constexpr (MODE == kFwd) {
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok && total > 0) {
+                // second use: every slice's sum of probabilities -> the row's normaliser and lse
+                constexpr int NPART = NG * NSPLIT;
                 red_buf[(NPART + grp * NSPLIT + sp) * 128 + row] = run_sum;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pw_all);
+                ok = pw_wait(bar_pw_all, pw_all_phase);
+                pw_all_phase ^= 1u;
+                float l = 0.f;
+                #pragma unroll
+                for (int k = 0; k < NPART; ++k) l += red_buf[(NPART + k) * 128 + row];
+                fwd_inv_l = (l > 0.f) ? 1.f / l : 0.f;
+                if (lse_writer && own_ok) p.lse[row_stat] = (l > 0.f) ? (log2f(l) - nL2) * kLn2 : -INFINITY;
             }
-            if (total > 0) pw_all_phase ^= 1u;       // one use of the all-groups barrier per item
         }
         float alpha = 0.f, ecirc = 0.f;
         ok = __all_sync(0xffffffffu, ok);
@@ -985,6 +996,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 float* a1 = EARLY ? acc1[EARLY ? c / 16 : 0] : late1;
                 if (!own_ok) continue;          // stores are per row
                 if constexpr (MODE == kFwd) {
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i) a0[i] *= fwd_inv_l;
                     store16_from_float<BF16>(p.res0, res_off + col, a0);
                 } else if constexpr (MODE == kBwd1Row) {
                     #pragma unroll
