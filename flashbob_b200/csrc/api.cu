@@ -11,7 +11,7 @@ namespace bob {
 
 enum : int {
     kErrNull = -1, kErrGeom = -2, kErrDtype = -3, kErrHeadDim = -4, kErrStride = -5,
-    kErrWorkspace = -6, kErrDevice = -7, kErrLaunch = -8, kErrAttr = -9, kErrAlign = -10,
+    kErrWorkspace = -6, kErrDevice = -7, kErrLaunch = -8, kErrAttr = -9, kErrAlign = -10, kErrRegs = -13,
     kErrNoDriver = -100,
 };
 
@@ -95,6 +95,16 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CFG::SMEM_BYTES) !=
         cudaSuccess)
         return kErrAttr;
+    if constexpr (CFG::REBALANCE) {
+        // The kernel's warpgroups trade registers after launch; the trade only balances (and the
+        // pointwise warps' request can only ever be met) if the kernel was built with the register
+        // count the trade assumes.  Refuse to launch otherwise.
+        static const int regs_at_launch = [&]() {
+            cudaFuncAttributes a;
+            return cudaFuncGetAttributes(&a, kernel) == cudaSuccess ? a.numRegs : 0;
+        }();
+        if (regs_at_launch * CFG::NTHREADS < 256 * CFG::REGS_POINTWISE + 128 * CFG::REGS_ROLE) return kErrRegs;
+    }
     // CTAs take work items in rounds (see the kernel): gridDim.x items per round.
     const int n_own = MT::COL ? g->Nk : g->Nq;
     const long long items = (long long)((n_own + 127) / 128) * (MT::COL ? g->Hkv : g->Hq) * g->B;
@@ -194,6 +204,7 @@ extern "C" const char* bob_sm100_error_string(int code) {
         case kErrLaunch: return "kernel launch failed";
         case kErrAttr: return "cannot raise the dynamic shared memory limit";
         case kErrAlign: return "tensor base address must be 16-byte aligned";
+        case kErrRegs: return "kernel was built with too few registers for its register rebalancing";
         case kErrNoDriver: return "cuTensorMapEncodeTiled is unavailable in this driver";
         case -11: return "cannot resolve the built-in scratch array on this device";
         case -12: return "problem too large for the built-in scratch (B*Hq*Nq > 1048576 rows)";

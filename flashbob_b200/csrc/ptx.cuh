@@ -73,6 +73,18 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Register rebalancing between warpgroups (four consecutive warps): every warp of a warpgroup gives
+// registers back to the CTA's pool, or takes registers from it (waits until they are there).  The
+// counts must add up to what the kernel was launched with.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ----------------------------------------------------------------------------------------
 // proxies and fences
 // ----------------------------------------------------------------------------------------
@@ -159,6 +171,13 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+        : "memory");
+}
+// Same for 4 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
         : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() {

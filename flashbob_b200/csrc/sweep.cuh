@@ -108,7 +108,12 @@ struct SweepConfig {
     static constexpr int NSPLIT = TN / CW;
     static constexpr int GP = 128 * NSPLIT;                // pointwise threads per group
     static constexpr int NPW = GP * NG;                    // pointwise threads
-    static constexpr int NTHREADS = NPW + 64;              // + MMA warp + TMA warp
+    // Second backward with 32 columns per pointwise thread: the two pointwise warpgroups take
+    // registers over from the warpgroup of the MMA and TMA warps (padded to four warps, two of them
+    // idle) once the kernel runs, which lets a pointwise thread hold a whole tile's score columns.
+    static constexpr bool REBALANCE = (MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32 && NG == 1 && NPW == 256;
+    static constexpr int NTHREADS = REBALANCE ? 384 : NPW + 64;   // + MMA warp + TMA warp (+ 2 idle warps)
+    static constexpr int REGS_POINTWISE = 224, REGS_ROLE = 56;     // 2 * 128 * 224 + 128 * 56 = 384 * 168
     static constexpr int KSUB = DPAD / 64;                 // 64-element sub-tiles along the head dim
     static constexpr int OWN_TILE_BYTES = 128 * 128 * KSUB;
     static constexpr int OTH_SUB_BYTES = TN * 128;         // one 64-element-wide sub-tile of a swept tensor
@@ -183,8 +188,7 @@ __global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN, NG, CW>::NTHREADS,
 sweep_kernel(const __grid_constant__ SweepParams p) {
     using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
     static_assert(CW == 16 || CW == 32, "16 or 32 columns per pointwise thread");
-    constexpr bool PREFETCH = false;           // keep the next round's loads in flight while computing
-    constexpr int RW = (CW == 32) ? 16 : 8;    // columns per round of tensor-memory loads
+    constexpr int RW = 16;                     // columns per round of tensor-memory loads
     using MT = ModeTraits<MODE>;
     constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, GP = CFG::GP, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
     constexpr bool COL = MT::COL;
@@ -232,6 +236,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     const int n_items = n_own_tiles * per_rank;
     const int n_outer = (MODE == kFwd) ? 2 : (COL ? p.G : 1);
     const int doff = p.delta_off;                // q_offset - k_offset, clamped to +-2^30 by the host
+    // kernel parameters that the per-tile code needs, read once
+    const bool causal = p.is_causal != 0;
+    const int window = p.window;
+    const bool has_uq = p.has_uq != 0, has_uk = p.has_uk != 0, has_uv = p.has_uv != 0;
     struct Item { int own0, head, batch, kv_head, t_lo, t_hi, T, total; };
     auto decode = [&](int item) {
         Item w;
@@ -240,18 +248,18 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         w.head = rem % grid_heads;               // query head (row-owned) or KV head (column-owned)
         w.batch = rem / grid_heads;
         // causal: row-owned sweeps grow with the row index, column-owned ones shrink with the column
-        const int own_tile = (!COL && p.is_causal) ? (n_own_tiles - 1 - tile_rank) : tile_rank;
+        const int own_tile = (!COL && causal) ? (n_own_tiles - 1 - tile_rank) : tile_rank;
         w.own0 = own_tile * 128;
         w.kv_head = COL ? w.head : w.head / p.G;
         int lo = 0, hi = n_oth;                  // other-side positions [lo, hi) that can be unmasked
         const int own_last = min(w.own0 + 127, n_own - 1);
-        if (p.is_causal) {
+        if (causal) {
             if (!COL) {
                 hi = (int)min((long long)n_oth, (long long)own_last + doff + 1);
-                if (p.window > 0) lo = (int)max(0LL, (long long)w.own0 + doff - p.window + 1);
+                if (window > 0) lo = (int)max(0LL, (long long)w.own0 + doff - window + 1);
             } else {
                 lo = (int)max(0LL, (long long)w.own0 - doff);
-                if (p.window > 0) hi = (int)min((long long)n_oth, (long long)own_last - doff + p.window);
+                if (window > 0) hi = (int)min((long long)n_oth, (long long)own_last - doff + window);
             }
         }
         w.t_lo = (hi > lo) ? lo / TN : 0;
@@ -308,13 +316,15 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     auto aborted = [&]() { return misc[1] != 0; };
 
     auto has_tensor = [&](int t) {
-        return t == kTUQ ? p.has_uq : (t == kTUK ? p.has_uk : (t == kTUV ? p.has_uv : 1));
+        return t == kTUQ ? has_uq : (t == kTUK ? has_uk : (t == kTUV ? has_uv : true));
     };
     // shared-memory address of sub-tile `sub` of swept-tensor slot `slot` in pipeline stage `stage`
     auto oth_addr = [&](int stage, int sub, int slot) {
         return sbase + CFG::OFF_OTH + stage * CFG::OTH_STAGE_BYTES + (sub * MT::NOTH + slot) * CFG::OTH_SUB_BYTES;
     };
 
+    if (warp >= NPW / 32) {
+    if constexpr (CFG::REBALANCE) setmaxnreg_dec<CFG::REGS_ROLE>();    // the whole warpgroup, idle warps too
     if (warp == NPW / 32 + 1) {
         // =========================== TMA producer =============================================
         // Lane 0 issues the TMA copies.  In column-owned modes all 32 lanes also stage the swept
@@ -472,18 +482,18 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     score_mma(NS1{}, sc, 1, 1, 1, s, false);     // dP = dO V^T     | dP^T = V dO^T
                 } else if constexpr (MODE == kBwd2Row) {
                     // own: Q, dO, uQ;  swept: K, uK, V, uV;  accumulators: S, F, dP, C
-                    if (p.has_uk) score_mma(NS2{}, sc, 0, 0, 0, s, false);      // S | F  = Q [K; uK]^T
+                    if (has_uk) score_mma(NS2{}, sc, 0, 0, 0, s, false);      // S | F  = Q [K; uK]^T
                     else          score_mma(NS1{}, sc, 0, 0, 0, s, false);      // S      = Q K^T
-                    if (p.has_uq) score_mma(NS1{}, sc, 1, 2, 0, s, p.has_uk);   // F     += uQ K^T
-                    if (p.has_uv) score_mma(NS2{}, sc, 2, 1, 2, s, false);      // dP | C = dO [V; uV]^T
+                    if (has_uq) score_mma(NS1{}, sc, 1, 2, 0, s, has_uk);   // F     += uQ K^T
+                    if (has_uv) score_mma(NS2{}, sc, 2, 1, 2, s, false);      // dP | C = dO [V; uV]^T
                     else          score_mma(NS1{}, sc, 2, 1, 2, s, false);      // dP     = dO V^T
                 } else {
                     // own: K, V, uK, uV;  swept: Q, uQ, dO;  accumulators: S^T, F^T, dP^T, C^T
-                    if (p.has_uq) score_mma(NS2{}, sc, 0, 0, 0, s, false);      // S^T | F^T = K [Q; uQ]^T
+                    if (has_uq) score_mma(NS2{}, sc, 0, 0, 0, s, false);      // S^T | F^T = K [Q; uQ]^T
                     else          score_mma(NS1{}, sc, 0, 0, 0, s, false);      // S^T       = K Q^T
-                    if (p.has_uk) score_mma(NS1{}, sc, 1, 2, 0, s, p.has_uq);   // F^T      += uK Q^T
+                    if (has_uk) score_mma(NS1{}, sc, 1, 2, 0, s, has_uq);   // F^T      += uK Q^T
                     score_mma(NS1{}, sc, 2, 1, 2, s, false);                    // dP^T      = V dO^T
-                    if (p.has_uv) score_mma(NS1{}, sc, 3, 3, 2, s, false);      // C^T       = uV dO^T
+                    if (has_uv) score_mma(NS1{}, sc, 3, 3, 2, s, false);      // C^T       = uV dO^T
                 }
                 if (elect_one()) umma_commit(bar_sc_full(g));
                 BOB_PH(2)
@@ -535,14 +545,14 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         out_mma(ob, 1, 0, 1, s, acc);                       // dV += P^T dO
                     } else if constexpr (MODE == kBwd2Row) {
                         // operands: P, P*F, P*T, dS;  swept: K, uK, V, uV;  outputs: dObar, Omega
-                        if (p.has_uv) out_mma(ob, 0, 0, 3, s, acc);         // dObar += P uV
-                        out_mma(ob, 0, 1, 2, s, acc || p.has_uv);           // dObar += (P*F) V
+                        if (has_uv) out_mma(ob, 0, 0, 3, s, acc);         // dObar += P uV
+                        out_mma(ob, 0, 1, 2, s, acc || has_uv);           // dObar += (P*F) V
                         out_mma(ob, 1, 2, 0, s, acc);                       // Omega += (P*T) K
-                        if (p.has_uk) out_mma(ob, 1, 3, 1, s, true);        // Omega += dS uK
+                        if (has_uk) out_mma(ob, 1, 3, 1, s, true);        // Omega += dS uK
                     } else {
                         // operands: Sbar^T, dS^T, (P*(F-alpha))^T;  outputs: Kbar, Vbar
                         out_mma(ob, 0, 0, 0, s, acc);                       // Kbar += Sbar^T Q
-                        if (p.has_uq) out_mma(ob, 0, 1, 1, s, true);        // Kbar += dS^T uQ
+                        if (has_uq) out_mma(ob, 0, 1, 1, s, true);        // Kbar += dS^T uQ
                         out_mma(ob, 1, 2, 2, s, acc);                       // Vbar += (P*(F-alpha))^T dO
                     }
                     if (elect_one()) umma_commit(bar_op_empty(g));
@@ -558,8 +568,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             }   // items
             BOB_PH_FLUSH(8, lane == 0)
         }
+    }
     } else {
         // =========================== pointwise threads =======================================
+        if constexpr (CFG::REBALANCE) setmaxnreg_inc<CFG::REGS_POINTWISE>();
         const int grp = tid / GP;                // pointwise group: takes iterations grp, grp + NG, ...
         const int gtid = tid % GP;
         const int row = gtid & 127;              // own row inside the tile == tensor-memory lane
@@ -687,15 +699,15 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             uint32_t vmask = kAllCols;
             if constexpr (!FULL) {
                 int mlo = 0, mhi = min(CW - 1, n_oth - (oth0 + col0) - 1);
-                if (p.is_causal) {
+                if (causal) {
                     if constexpr (!COL) {
                         const int d0 = own_idx + doff - (oth0 + col0);       // dist falls with the column
                         mhi = min(mhi, d0);
-                        if (p.window > 0) mlo = max(mlo, d0 - p.window + 1);
+                        if (window > 0) mlo = max(mlo, d0 - window + 1);
                     } else {
                         const int d0 = (oth0 + col0) + doff - own_idx;       // dist grows with the column
                         mlo = max(mlo, -d0);
-                        if (p.window > 0) mhi = min(mhi, p.window - 1 - d0);
+                        if (window > 0) mhi = min(mhi, window - 1 - d0);
                     }
                 }
                 vmask = (own_ok && mhi >= mlo) ? ((kAllCols >> (CW - 1 - mhi)) & (kAllCols << mlo)) : 0u;
@@ -737,15 +749,20 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 for (int h = 0; h < CW / 16; ++h) tmem_st8(op_taddr + 8 * h, w0 + 8 * h);
             } else {
                 // accumulator order: S, dP (first backward) or S, F, dP, C (second backward).
-                // My CW columns are taken in rounds of 8 to bound the live registers; the score
-                // accumulators are handed back as soon as the last round is loaded.
+                // My CW columns are taken in rounds of RW.  LOAD_ALL (second backward, 32 columns per
+                // thread): every round's loads are issued at once and the score accumulators are
+                // handed back before any arithmetic, so that the next tile's score products run
+                // under this tile's arithmetic.  Otherwise one round is in registers at a time and
+                // the accumulators are handed back when the last round has been loaded.  Each round's
+                // packed operands go to tensor memory as soon as they are formed.
                 constexpr int R = CW / RW;
+                constexpr bool LOAD_ALL = BWD2 && CW == 32;
+                constexpr int NB = LOAD_ALL ? R : 1;
                 const float2 cexp2 = make_float2(c_exp, c_exp);
                 const float2 scale2 = make_float2(p.scale, p.scale);
-                const bool has_f = BWD2 && (p.has_uq || p.has_uk);
-                const bool has_c = BWD2 && p.has_uv;
-                uint32_t w0[CW / 2], w1[CW / 2], w2[CW / 2], w3[CW / 2];
-                float in_s[2][RW], in_dp[2][RW], in_f[2][RW], in_c[2][RW];
+                const bool has_f = BWD2 && (has_uq || has_uk);
+                const bool has_c = BWD2 && has_uv;
+                float in_s[NB][RW], in_dp[NB][RW], in_f[NB][RW], in_c[NB][RW];
                 auto issue_loads = [&](int r, int b) {
                     const int cb = col0 + RW * r;
                     auto ld = [&](uint32_t addr, float* dst) {
@@ -758,19 +775,25 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         if (has_c) ld(tsc + 3 * TN + cb, in_c[b]);
                     }
                 };
-                issue_loads(0, 0);
+                auto release_scores = [&]() {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_sc_empty(grp));
+                };
+                if constexpr (LOAD_ALL) {
+                    #pragma unroll
+                    for (int r = 0; r < R; ++r) issue_loads(r, r);
+                } else {
+                    issue_loads(0, 0);
+                }
                 #pragma unroll
                 for (int half = 0; half < R; ++half) {            // `half` = round of RW columns
                     const int cb = col0 + RW * half;
-                    const int b = PREFETCH ? (half & 1) : 0;
-                    tmem_wait_ld();
-                    BOB_PH(1)
-                    if (half + 1 < R) {
-                        if constexpr (PREFETCH) issue_loads(half + 1, (half + 1) & 1);
-                    } else {
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_sc_empty(grp));
+                    const int b = LOAD_ALL ? half : 0;
+                    if (!LOAD_ALL || half == 0) {
+                        tmem_wait_ld();
+                        BOB_PH(1)
+                        if (LOAD_ALL || half + 1 == R) release_scores();
                     }
                     float* s_ = in_s[b];
                     float* dp_ = in_dp[b];
@@ -786,6 +809,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                             for (int c = 0; c < RW; ++c) cc_[c] = 0.f;
                         }
                     }
+                    uint32_t w0[RW / 2], w1[RW / 2], w2[RW / 2], w3[RW / 2];
+                    (void)w2; (void)w3;
                     // negated statistics of these columns (column-owned modes), four columns per load
                     const float4* sb4 = reinterpret_cast<const float4*>(stat_buf + stage * 4 * TN + cb);
                     #pragma unroll
@@ -797,10 +822,11 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         }
                         #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const int c = 4 * c4 + 2 * h;          // columns c, c + 1 of this half
-                            const int wi = (RW / 2) * half + (c >> 1);   // packed word index among my CW columns
-                            const int mc = RW * half + c;                // bit index in vmask
+                            const int c = 4 * c4 + 2 * h;          // columns c, c + 1 of this round
+                            const int wi = c >> 1;                 // packed word index inside this round
+                            const int mc = RW * half + c;          // bit index in vmask
                             float2 nl2, ndl, nal, nec;
+                            (void)nal; (void)nec;
                             if constexpr (COL) {
                                 nl2 = h ? make_float2(q_l2.z, q_l2.w) : make_float2(q_l2.x, q_l2.y);
                                 ndl = h ? make_float2(q_dl.z, q_dl.w) : make_float2(q_dl.x, q_dl.y);
@@ -852,19 +878,25 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                             }
                         }
                     }
-                    if constexpr (!PREFETCH) {
+                    if constexpr (!LOAD_ALL) {
                         if (half + 1 < R) issue_loads(half + 1, 0);
                     }
-                }
-                BOB_PH(2)
-                if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
-                BOB_PH(3)
-                #pragma unroll
-                for (int h = 0; h < CW / 16; ++h) {
-                    tmem_st8(op_taddr + 0 * CFG::OPER_COLS_EACH + 8 * h, w0 + 8 * h);
-                    if constexpr (MT::NOPER > 1) tmem_st8(op_taddr + 1 * CFG::OPER_COLS_EACH + 8 * h, w1 + 8 * h);
-                    if constexpr (MT::NOPER > 2) tmem_st8(op_taddr + 2 * CFG::OPER_COLS_EACH + 8 * h, w2 + 8 * h);
-                    if constexpr (MT::NOPER > 3) tmem_st8(op_taddr + 3 * CFG::OPER_COLS_EACH + 8 * h, w3 + 8 * h);
+                    if (half == 0) {
+                        BOB_PH(2)
+                        // the previous tile's output products must have consumed its operands
+                        if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
+                        BOB_PH(3)
+                    }
+                    {
+                        const uint32_t dst = op_taddr + (RW / 2) * half;     // RW / 2 packed words per round
+                        auto st = [&](uint32_t addr, const uint32_t* w) {
+                            if constexpr (RW == 16) tmem_st8(addr, w); else tmem_st4(addr, w);
+                        };
+                        st(dst + 0 * CFG::OPER_COLS_EACH, w0);
+                        if constexpr (MT::NOPER > 1) st(dst + 1 * CFG::OPER_COLS_EACH, w1);
+                        if constexpr (MT::NOPER > 2) st(dst + 2 * CFG::OPER_COLS_EACH, w2);
+                        if constexpr (MT::NOPER > 3) st(dst + 3 * CFG::OPER_COLS_EACH, w3);
+                    }
                 }
             }
             tmem_wait_st();
@@ -878,17 +910,34 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
 
         BOB_PH(6)
         {
+            // swept tiles [full_lo, full_hi) pair with my own tile entirely unmasked and in range
+            int full_lo = 0, full_hi = 0;
+            if (own0 + 127 < n_own) {
+                long long lo = 0, hi = n_oth / TN;                  // tiles that lie inside the tensor
+                if (causal) {
+                    // oldest and newest own position of the tile pair against the swept tile's extremes
+                    if constexpr (!COL) {
+                        hi = min(hi, ((long long)own0 + doff + 1) / TN);                          // dist >= 0 everywhere
+                        if (window > 0) {
+                            const long long x = (long long)own0 + 127 + doff - window;            // last swept position with dist >= window
+                            lo = max(lo, x < 0 ? 0LL : (x + TN) / TN);
+                        }
+                    } else {
+                        const long long a = (long long)own0 + 127 - doff;                         // first swept position with dist >= 0
+                        lo = max(lo, a <= 0 ? 0LL : (a + TN - 1) / TN);
+                        if (window > 0) {
+                            const long long b = (long long)own0 - doff + window;                  // one past the last with dist < window
+                            hi = min(hi, b <= 0 ? 0LL : b / TN);
+                        }
+                    }
+                }
+                if (hi > lo) { full_lo = (int)lo; full_hi = (int)hi; }
+            }
             int tile = t_lo, outer = 0;
             for (int it = 0; ok && it < total; ++it) {
                 if ((cnt + it) % NG == grp) {            // my group's turn
                     // is the whole 128 x TN tile pair unmasked and inside both tensors?  (uniform per CTA)
-                    const int oth0 = tile * TN;
-                    bool full = (own0 + 127 < n_own) && (oth0 + TN <= n_oth);
-                    if (p.is_causal) {
-                        const int dmin = COL ? (oth0 + doff - (own0 + 127)) : (own0 + doff - (oth0 + TN - 1));
-                        const int dmax = COL ? (oth0 + TN - 1 + doff - own0) : (own0 + 127 + doff - oth0);
-                        full = full && dmin >= 0 && (p.window == 0 || dmax < p.window);
-                    }
+                    const bool full = tile >= full_lo && tile < full_hi;
                     ok = full ? tile_body(BoolTag<true>{}, it, cnt + it, tile, outer, stage, round)
                               : tile_body(BoolTag<false>{}, it, cnt + it, tile, outer, stage, round);
                 }
