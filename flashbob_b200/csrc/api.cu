@@ -155,7 +155,8 @@ static int bwd2_kernel_mask() {
     return 3;
 }
 
-// Builds with BOB_PHASE_TIMERS read a device pointer (hex) from BOB_SM100_PHASE_PTR: 16 counters.
+// Builds with BOB_PHASE_TIMERS read a device pointer (hex) from BOB_SM100_PHASE_PTR: 24 counters
+// (12 of a pointwise thread, then 12 of the MMA warp).
 static long long* phase_pointer() {
 #ifdef BOB_PHASE_TIMERS
     const char* e = std::getenv("BOB_SM100_PHASE_PTR");

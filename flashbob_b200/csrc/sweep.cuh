@@ -31,9 +31,9 @@ namespace bob {
 // Optional in-kernel phase timers: with -DBOB_PHASE_TIMERS one pointwise thread and the MMA issuer of
 // every CTA add the SM cycles they spend in each phase to SweepParams::phase_cycles[0..15].
 #ifdef BOB_PHASE_TIMERS
-#define BOB_PH_DECL long long ph_t = clock64(); long long ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define BOB_PH_DECL long long ph_t = clock64(); long long ph_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #define BOB_PH(i) { const long long ph_n = clock64(); ph_acc[i] += ph_n - ph_t; ph_t = ph_n; }
-#define BOB_PH_FLUSH(base, on) if ((on) && p.phase_cycles) { for (int ph_i = 0; ph_i < 8; ++ph_i) atomicAdd(reinterpret_cast<unsigned long long*>(p.phase_cycles) + (base) + ph_i, (unsigned long long)ph_acc[ph_i]); }
+#define BOB_PH_FLUSH(base, on) if ((on) && p.phase_cycles) { for (int ph_i = 0; ph_i < 12; ++ph_i) atomicAdd(reinterpret_cast<unsigned long long*>(p.phase_cycles) + (base) + ph_i, (unsigned long long)ph_acc[ph_i]); }
 #else
 #define BOB_PH_DECL
 #define BOB_PH(i)
@@ -113,7 +113,13 @@ struct SweepConfig {
     // idle) once the kernel runs, which lets a pointwise thread hold a whole tile's score columns.
     static constexpr bool REBALANCE = (MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32 && NG == 1 && NPW == 256;
     static constexpr int NTHREADS = REBALANCE ? 384 : NPW + 64;   // + MMA warp + TMA warp (+ 2 idle warps)
-    static constexpr int REGS_POINTWISE = 224, REGS_ROLE = 56;     // 2 * 128 * 224 + 128 * 56 = 384 * 168
+#ifndef BOB_REGS_POINTWISE
+#define BOB_REGS_POINTWISE 224
+#define BOB_REGS_ROLE 56
+#endif
+    static constexpr int REGS_POINTWISE = BOB_REGS_POINTWISE, REGS_ROLE = BOB_REGS_ROLE;
+    static_assert(2 * 128 * REGS_POINTWISE + 128 * REGS_ROLE <= 384 * 168 && REGS_POINTWISE % 8 == 0 && REGS_ROLE % 8 == 0,
+                  "register rebalancing must fit the pool of 384 threads x 168 registers");
     static constexpr int KSUB = DPAD / 64;                 // 64-element sub-tiles along the head dim
     static constexpr int OWN_TILE_BYTES = 128 * 128 * KSUB;
     static constexpr int OTH_SUB_BYTES = TN * 128;         // one 64-element-wide sub-tile of a swept tensor
@@ -128,7 +134,14 @@ struct SweepConfig {
     static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
     // as many stages of swept tiles as shared memory allows, between 2 and 6: the TMA latency of a
     // tile (~2 us) hides behind the tiles before it
-    static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + 16 * 1024;
+    // Row-owned second backward at head dim <= 64: the epilogue's global operands (out, dQ: 16-bit,
+    // 16 KB each; pk: fp32, 32 KB) are copied into shared memory with coalesced asynchronous copies
+    // while the item runs, and the results leave through the same buffers with coalesced stores.
+    // (A thread owns one row of the tile; touching global memory row by row costs one 128-byte line
+    // per lane and instruction.)
+    static constexpr bool STAGED_IO = (MODE == kBwd2Row) && DPAD == 64 && NG == 1;
+    static constexpr int IO_BYTES = STAGED_IO ? 64 * 1024 : 0;
+    static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + 16 * 1024 + IO_BYTES;
     static constexpr int STAGE_ROOM = (232448 - FIXED_BYTES) / OTH_STAGE_BYTES;
     static constexpr int STAGE_MAX = 6;
     static constexpr int NSTAGE = STAGE_ROOM >= STAGE_MAX ? STAGE_MAX : (STAGE_ROOM >= 2 ? STAGE_ROOM : 2);
@@ -140,7 +153,8 @@ struct SweepConfig {
     static constexpr int OFF_BAR = OFF_RED + 2 * NG * NSPLIT * 128 * 4;
     static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag
-    static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;                     // + alignment slack
+    static constexpr int OFF_IO = (OFF_MISC + 16 + 127) & ~127;                 // staged epilogue operands
+    static constexpr int SMEM_BYTES = OFF_IO + IO_BYTES + 1024;                 // + alignment slack
     static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
 };
 
@@ -164,6 +178,21 @@ __device__ __forceinline__ void load16_as_float(const void* base, long long elem
         } else {
             __half2 t = *reinterpret_cast<const __half2*>(&w[i]);
             float2 f = __half22float2(t);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+}
+
+template <bool BF16>
+__device__ __forceinline__ void unpack8_as_float(const uint4 a, float* v) {
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (BF16) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
             v[2 * i] = f.x; v[2 * i + 1] = f.y;
         }
     }
@@ -566,7 +595,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             if (elect_one()) umma_commit(bar_done);
             ++n_live;
             }   // items
-            BOB_PH_FLUSH(8, lane == 0)
+            BOB_PH_FLUSH(12, lane == 0)
         }
     }
     } else {
@@ -654,6 +683,30 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
         if constexpr (MODE == kBwd2Row) {
             if (own_ok) { nL2 = -p.lse[row_stat] * kLog2e; ndlt = -p.delta[row_stat]; }
+        }
+        // staged epilogue operands: 16-byte chunk c of row r sits at chunk position c ^ (r & 7) of
+        // its 128-byte line, so that both the row-wise and the chunk-wise accesses are conflict-free
+        const uint32_t io_out = sbase + CFG::OFF_IO, io_dq = io_out + 16384, io_pk = io_out + 32768;
+        const long long tile_row0 = ((long long)batch * p.Hq + head) * p.Nq + own0;   // first row of the contiguous results
+        if constexpr (CFG::STAGED_IO) {
+            const uint16_t* g_out = static_cast<const uint16_t*>(p.out) + (long long)batch * p.out_sb + (long long)head * p.out_sh + (long long)own0 * p.out_sn;
+            const uint16_t* g_dq = static_cast<const uint16_t*>(p.dQ) + (long long)batch * p.dQ_sb + (long long)head * p.dQ_sh + (long long)own0 * p.dQ_sn;
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int id = tid + 256 * k, r = id >> 3, c = id & 7;
+                if (own0 + r < n_own && c * 8 < p.D) {
+                    const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
+                    cp_async16(io_out + off, g_out + (long long)r * p.out_sn + c * 8);
+                    cp_async16(io_dq + off, g_dq + (long long)r * p.dQ_sn + c * 8);
+                }
+            }
+            #pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int id = tid + 256 * k, r = id >> 4, c = id & 15;
+                if (own0 + r < n_own && c * 4 < p.D)
+                    cp_async16(io_pk + r * 256 + ((c & 8) << 4) + (((c ^ r) & 7) << 4), p.pk + (tile_row0 + r) * p.D + c * 4);
+            }
+            cp_async_commit();
         }
 
         bool fwd_combined = false;               // forward: first-sweep maxima already combined
@@ -983,6 +1036,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             constexpr int NPART = NG * NSPLIT;          // every pointwise thread of my row holds a partial sum
             red_buf[(grp * NSPLIT + sp) * 128 + row] = acc_a.x + acc_a.y;
             red_buf[(NPART + grp * NSPLIT + sp) * 128 + row] = acc_b.x + acc_b.y;
+            if constexpr (CFG::STAGED_IO) cp_async_wait_all();      // my copies; the barrier below publishes them
             if (ok) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pw_all);
@@ -993,8 +1047,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             for (int k = 0; k < NPART; ++k) { alpha += red_buf[k * 128 + row]; ecirc += red_buf[(NPART + k) * 128 + row]; }
             if (ok && grp == 0 && sp == 0 && own_ok) { p.alpha[row_stat] = alpha; p.ecirc[row_stat] = ecirc; }
         }
+        BOB_PH(8)
         if (ok && total > 0) ok = pw_wait(bar_done, n_live & 1);
         tc_fence_after_sync();
+        BOB_PH(9)
         if (ok) {
             constexpr int DC = DPAD / (NSPLIT * NG);    // output columns per pointwise thread
             constexpr int NCH = DC / 16;
@@ -1025,6 +1081,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             };
             bool released = false;
             if (EARLY && total > 0) { release_outputs(); released = true; }
+            BOB_PH(10)
             #pragma unroll
             for (int c = 0; c < DC; c += 16) {
                 const int col = (grp * NSPLIT + sp) * DC + c;
@@ -1066,33 +1123,80 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 } else {
                     // accumulators: a0 = P uV + (P*F) V, a1 = (P*T) K + dS uK;  PK comes from the first backward
                     float o[16], g[16], pkv[16];
-                    {
+                    if constexpr (CFG::STAGED_IO) {
+                        const uint32_t sw = row & 7;
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int c = col / 4 + i;                         // 16-byte chunk of the fp32 row
+                            const uint4 t = ld_shared_v4(io_pk + row * 256 + ((c & 8) << 4) + (((c ^ sw) & 7) << 4));
+                            pkv[4 * i] = __uint_as_float(t.x); pkv[4 * i + 1] = __uint_as_float(t.y);
+                            pkv[4 * i + 2] = __uint_as_float(t.z); pkv[4 * i + 3] = __uint_as_float(t.w);
+                        }
+                        #pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const uint32_t off = row * 128 + (((col / 8 + i) ^ sw) << 4);
+                            unpack8_as_float<BF16>(ld_shared_v4(io_out + off), o + 8 * i);
+                            unpack8_as_float<BF16>(ld_shared_v4(io_dq + off), g + 8 * i);
+                        }
+                    } else {
                         const float4* src = reinterpret_cast<const float4*>(p.pk + res_off + col);
                         #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const float4 t = src[i];
                             pkv[4 * i] = t.x; pkv[4 * i + 1] = t.y; pkv[4 * i + 2] = t.z; pkv[4 * i + 3] = t.w;
                         }
+                        load16_as_float<BF16>(p.out, (long long)batch * p.out_sb + (long long)head * p.out_sh +
+                                                         (long long)own_idx * p.out_sn + col, o);
+                        load16_as_float<BF16>(p.dQ, (long long)batch * p.dQ_sb + (long long)head * p.dQ_sh +
+                                                        (long long)own_idx * p.dQ_sn + col, g);
                     }
-                    load16_as_float<BF16>(p.out, (long long)batch * p.out_sb + (long long)head * p.out_sh +
-                                                     (long long)own_idx * p.out_sn + col, o);
-                    load16_as_float<BF16>(p.dQ, (long long)batch * p.dQ_sb + (long long)head * p.dQ_sh +
-                                                    (long long)own_idx * p.dQ_sn + col, g);
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const float dob = a0[i] - alpha * o[i];                                   // dObar
                         const float qb = p.scale * (a1[i] - ecirc * pkv[i]) - alpha * g[i];       // Qbar
                         a0[i] = qb; a1[i] = dob;
                     }
-                    store16_from_float<BF16>(p.res0, res_off + col, a0);
-                    store16_from_float<BF16>(p.res1, res_off + col, a1);
+                    if constexpr (CFG::STAGED_IO) {
+                        // results replace my own chunks of the staged operands: Qbar over dQ, dObar over out
+                        #pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const uint32_t off = row * 128 + (((col / 8 + i) ^ (row & 7)) << 4);
+                            st_shared_v4(io_dq + off, pack2<BF16>(a0[8 * i], a0[8 * i + 1]), pack2<BF16>(a0[8 * i + 2], a0[8 * i + 3]),
+                                         pack2<BF16>(a0[8 * i + 4], a0[8 * i + 5]), pack2<BF16>(a0[8 * i + 6], a0[8 * i + 7]));
+                            st_shared_v4(io_out + off, pack2<BF16>(a1[8 * i], a1[8 * i + 1]), pack2<BF16>(a1[8 * i + 2], a1[8 * i + 3]),
+                                         pack2<BF16>(a1[8 * i + 4], a1[8 * i + 5]), pack2<BF16>(a1[8 * i + 6], a1[8 * i + 7]));
+                        }
+                    } else {
+                        store16_from_float<BF16>(p.res0, res_off + col, a0);
+                        store16_from_float<BF16>(p.res1, res_off + col, a1);
+                    }
                 }
             }
             if (total > 0 && !released) release_outputs();   // a thread with no column inside the head dim
         }
+        if constexpr (CFG::STAGED_IO) {
+            // every row's results are in shared memory: write the tile out, 16 bytes per thread and
+            // pass, whole 128-byte lines per quarter warp
+            if (ok) ok = pw_sync();
+            if (ok) {
+                uint16_t* g_q = static_cast<uint16_t*>(p.res0) + tile_row0 * p.D;
+                uint16_t* g_do = static_cast<uint16_t*>(p.res1) + tile_row0 * p.D;
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int id = tid + 256 * k, r = id >> 3, c = id & 7;
+                    if (own0 + r < n_own && c * 8 < p.D) {
+                        const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
+                        *reinterpret_cast<uint4*>(g_q + (long long)r * p.D + c * 8) = ld_shared_v4(io_dq + off);
+                        *reinterpret_cast<uint4*>(g_do + (long long)r * p.D + c * 8) = ld_shared_v4(io_out + off);
+                    }
+                }
+                ok = pw_sync();      // the buffers are free for the next item's copies
+            }
+        }
         if (total > 0) ++n_live;
         BOB_PH(5)
         }   // items
+        if constexpr (CFG::STAGED_IO) cp_async_wait_all();
         BOB_PH_FLUSH(0, tid == 0)
     }
 #undef BOB_ITEM_LOCALS
