@@ -919,12 +919,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                                 w2[wi] = pack2<BF16>(pt.x, pt.y);                         // P*T
                                 w3[wi] = pack2<BF16>(ds.x, ds.y);                         // dS
                             } else {
-                                const float2 f = __fmul2_rn(make_float2(f_[c], f_[c + 1]), scale2);
-                                const float2 t = __ffma2_rn(f, dps, make_float2(cc_[c], cc_[c + 1]));
-                                const float2 u = __fadd2_rn(__ffma2_rn(nal, dps, t), nec);   // T - alpha (dP - delta) - ecirc
+                                // T - alpha (dP - delta) - ecirc = (F - alpha) (dP - delta) + (C - ecirc)
+                                const float2 fa = __ffma2_rn(make_float2(f_[c], f_[c + 1]), scale2, nal);   // F - alpha
+                                const float2 u = __ffma2_rn(fa, dps, __fadd2_rn(make_float2(cc_[c], cc_[c + 1]), nec));
                                 const float2 sbar = __fmul2_rn(pr, u);
                                 const float2 ds = __fmul2_rn(pr, dps);
-                                const float2 ph = __fmul2_rn(pr, __fadd2_rn(f, nal));
+                                const float2 ph = __fmul2_rn(pr, fa);
                                 w0[wi] = pack2<BF16>(sbar.x, sbar.y);                     // Sbar^T
                                 w1[wi] = pack2<BF16>(ds.x, ds.y);                         // dS^T
                                 w2[wi] = pack2<BF16>(ph.x, ph.y);                         // (P*(F-alpha))^T
