@@ -128,7 +128,11 @@ struct SweepConfig {
     static constexpr int SC_COLS = MT::NSC * TN;
     static constexpr int OPER_COLS_EACH = TN / 2;          // 128 x TN 16-bit values, two per 32-bit column
     static constexpr int OPER_COLS = MT::NOPER * OPER_COLS_EACH;
-    static constexpr int OUT_COLS = MT::NOUT * DPAD;
+    // The forward keeps one output accumulator per pointwise group (each group runs its own online
+    // softmax over the tiles it takes; the epilogue merges them).
+    static constexpr int NACC = (MODE == kFwd) ? NG : MT::NOUT;
+    static_assert(MODE != kFwd || (NG == 2 && CW == TN), "forward: two groups, one thread per row");
+    static constexpr int OUT_COLS = NACC * DPAD;
     static constexpr int TMEM_NEED = NG * (SC_COLS + OPER_COLS) + OUT_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
     static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
@@ -150,7 +154,7 @@ struct SweepConfig {
     static constexpr int OFF_OTH = OFF_OWN + MT::NOWN * OWN_TILE_BYTES;
     static constexpr int OFF_STAT = OFF_OTH + NSTAGE * OTH_STAGE_BYTES;         // [NSTAGE][4][TN] floats
     static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [2][NG * NSPLIT][128] floats
-    static constexpr int OFF_BAR = OFF_RED + 2 * NG * NSPLIT * 128 * 4;
+    static constexpr int OFF_BAR = OFF_RED + (MODE == kFwd ? 4 : 2) * NG * NSPLIT * 128 * 4;   // forward: two copies
     static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag
     static constexpr int OFF_IO = (OFF_MISC + 16 + 127) & ~127;                 // staged epilogue operands
@@ -216,7 +220,7 @@ template <int MODE, int DPAD, int TN, bool BF16, int NG, int CW>
 __global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN, NG, CW>::NTHREADS, 1)
 sweep_kernel(const __grid_constant__ SweepParams p) {
     using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
-    static_assert(CW == 16 || CW == 32, "16 or 32 columns per pointwise thread");
+    static_assert(CW == 16 || CW == 32 || (CW == 64 && MODE == kFwd), "16 or 32 columns per pointwise thread (forward: 64)");
     constexpr int RW = 16;                     // columns per round of tensor-memory loads
     using MT = ModeTraits<MODE>;
     constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, GP = CFG::GP, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
@@ -263,7 +267,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     const int grid_heads = COL ? p.Hkv : p.Hq;
     const int per_rank = grid_heads * p.B;
     const int n_items = n_own_tiles * per_rank;
-    const int n_outer = (MODE == kFwd) ? 2 : (COL ? p.G : 1);
+    const int n_outer = COL ? p.G : 1;
     const int doff = p.delta_off;                // q_offset - k_offset, clamped to +-2^30 by the host
     // kernel parameters that the per-tile code needs, read once
     const bool causal = p.is_causal != 0;
@@ -404,14 +408,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     uint32_t bytes = 0;
                     #pragma unroll
                     for (int i = 0; i < MT::NOTH; ++i) {
-                        if (MODE == kFwd && outer == 0 && i == 1) continue;     // the statistics sweep needs K only
                         if (has_tensor(other_tensor<MODE>(i))) bytes += KSUB * CFG::OTH_SUB_BYTES;
                     }
                     mbar_arrive_expect_tx(bar_full(s), bytes);
                     #pragma unroll
                     for (int i = 0; i < MT::NOTH; ++i) {
                         const int t = other_tensor<MODE>(i);
-                        if (MODE == kFwd && outer == 0 && i == 1) continue;
                         if (!has_tensor(t)) continue;
                         #pragma unroll
                         for (int ks = 0; ks < KSUB; ++ks)
@@ -549,7 +551,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 if (nstage == NSTAGE) { nstage = 0; ++nround; }
                 if (it + 1 < total && !issue_scores(cnt + it + 1, nstage, nround)) { ok = false; break; }
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
-                const bool has_out = (MODE != kFwd) || it >= T;
+                const bool has_out = true;
                 if (has_out) {
                     const int g = (cnt + it) % NG;
                     const uint32_t ob = tmem_oper + g * CFG::OPER_COLS;
@@ -565,7 +567,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     tc_fence_after_sync();
                     const bool acc = n_out > 0;
                     if constexpr (MODE == kFwd) {
-                        out_mma(ob, 0, 0, 1, s, acc);                       // O += P V
+                        out_mma(ob, g, 0, 1, s, n_out >= NG);               // O_g += P V (group g's own accumulator)
                     } else if constexpr (MODE == kBwd1Row) {
                         out_mma(ob, 0, 0, 0, s, acc);                       // dQ += dS K
                         if (p.pk) out_mma(ob, 1, 1, 0, s, acc);             // PK += P K
@@ -636,6 +638,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         int stage = 0, round = 0;                // pipeline stage of tile `cnt`, and cnt / NSTAGE
         int n_op = 0;                            // operand rounds my group has written so far
         int n_live = 0;                          // items with at least one tile finished so far
+        int n_items_done = 0;                    // items finished so far, with or without tiles
         BOB_PH_DECL
 
         for (int r = 0; ok && r < n_rounds; ++r) {
@@ -650,7 +653,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         // per-row state (row-owned modes): -lse*log2e and -delta of my row
         float nL2 = 0.f, ndlt = 0.f;
         float2 acc_a = make_float2(0.f, 0.f), acc_b = make_float2(0.f, 0.f);   // row sums alpha, ecirc
-        float run_max = -1e30f, run_sum = 0.f;                                 // forward statistics sweep
+        // forward: my group's online softmax over the tiles it takes.  m_ref is the exponent reference
+        // (log2 units): it follows the running maximum only when that has grown by more than 8, so
+        // that the output accumulator rarely needs rescaling; probabilities stay below 2^8.
+        float m_ref = -1e30f, l_run = 0.f;
+        int n_op_item = 0;                       // tiles my group has finished in this item
+        (void)m_ref; (void)l_run; (void)n_op_item;
 
         if constexpr (MODE == kBwd1Row) {
             // delta = rowsum(dO * out), each slice sums its share of the head dim
@@ -709,32 +717,11 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             cp_async_commit();
         }
 
-        bool fwd_combined = false;               // forward: first-sweep maxima already combined
-        bool lse_writer = false;                 // forward: this thread writes the row's lse
 
         // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
         auto tile_body = [&](auto full_tag, int it, int gcnt, int tile, int outer, int stage, int round) -> bool {
             constexpr bool FULL = decltype(full_tag)::value;
             const int oth0 = tile * TN;
-
-            if constexpr (MODE == kFwd) {
-                if (outer == 1 && !fwd_combined) {
-                    // between the two sweeps: combine every slice's maximum into the row maximum.
-                    // Each pointwise thread of the CTA arrives once: here, before its first tile of
-                    // the second sweep, or after its loop if it has no such tile.
-                    constexpr int NPART = NG * NSPLIT;
-                    red_buf[(grp * NSPLIT + sp) * 128 + row] = run_max;
-                    fwd_combined = true;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_pw_all);
-                    if (!pw_wait(bar_pw_all, pw_all_phase)) return false;
-                    float m = -1e30f;
-                    #pragma unroll
-                    for (int k = 0; k < NPART; ++k) m = fmaxf(m, red_buf[k * 128 + row]);
-                    nL2 = -m;                            // second sweep: p = exp2(s - max), summed as it goes
-                    lse_writer = (it == T && sp == 0);   // exactly one thread per row
-                }
-            }
 
             BOB_PH(7)
             if constexpr (COL) {
@@ -748,8 +735,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             // ---- which of my 16 columns are unmasked: bits [mlo, mhi] of vmask ----------------
             // dist = query position - key position; unmasked iff in range and, when causal,
             // 0 <= dist (< window)
-            constexpr uint32_t kAllCols = (CW == 32) ? 0xFFFFFFFFu : 0xFFFFu;
-            uint32_t vmask = kAllCols;
+            using mask_t = typename std::conditional<(CW > 32), unsigned long long, uint32_t>::type;
+            constexpr mask_t kAllCols = (CW == 64) ? ~mask_t(0) : ((CW == 32) ? mask_t(0xFFFFFFFFu) : mask_t(0xFFFFu));
+            mask_t vmask = kAllCols;
             if constexpr (!FULL) {
                 int mlo = 0, mhi = min(CW - 1, n_oth - (oth0 + col0) - 1);
                 if (causal) {
@@ -763,43 +751,70 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         if (window > 0) mhi = min(mhi, window - 1 - d0);
                     }
                 }
-                vmask = (own_ok && mhi >= mlo) ? ((kAllCols >> (CW - 1 - mhi)) & (kAllCols << mlo)) : 0u;
+                vmask = (own_ok && mhi >= mlo) ? ((kAllCols >> (CW - 1 - mhi)) & (kAllCols << mlo)) : mask_t(0);
             }
 
             if constexpr (MODE == kFwd) {
+                // One thread owns a whole row of the tile.
                 float s_[CW];
                 #pragma unroll
-                for (int h = 0; h < CW / 16; ++h) tmem_ld16(tsc + col0 + 16 * h, s_ + 16 * h);
+                for (int h = 0; h < CW / 16; ++h) tmem_ld16(tsc + 16 * h, s_ + 16 * h);
                 tmem_wait_ld();
+                BOB_PH(1)
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_sc_empty(grp));
-                if (outer == 0) {
-                    // first sweep: the row maximum only (no exponentials)
-                    float mx = run_max;
-                    #pragma unroll
-                    for (int c = 0; c < CW; ++c)
-                        mx = fmaxf(mx, (FULL || ((vmask >> c) & 1u)) ? s_[c] * c_exp : -1e30f);
-                    run_max = mx;
-                    return true;
-                }
-                // second sweep: unnormalised probabilities relative to the row maximum; their sum
-                // normalises the output in the epilogue
+                // largest unmasked score of my row in this tile (the scale is positive)
+                float mr = -3.0e38f;
+                #pragma unroll
+                for (int c = 0; c < CW; ++c)
+                    mr = fmaxf(mr, (FULL || ((vmask >> c) & 1)) ? s_[c] : -3.0e38f);
+                const float mt = fmaxf(mr * c_exp, -1e30f);
+                // move the reference only when the maximum has outgrown it; the whole warp then
+                // rescales its rows of the output accumulator (factor 1 where nothing changed)
+                const bool grow = mt > m_ref + 8.f;
+                const bool rescale = __any_sync(0xffffffffu, grow) && n_op_item > 0;
+                float factor = 1.f;
+                if (grow) { factor = fast_exp2(m_ref - mt); m_ref = mt; }
+                l_run *= factor;
+                const float nm = -m_ref;
                 uint32_t w0[CW / 2];
+                float2 sum2 = make_float2(0.f, 0.f);
+                const float2 cexp2 = make_float2(c_exp, c_exp), nm2 = make_float2(nm, nm);
                 #pragma unroll
                 for (int c2 = 0; c2 < CW / 2; ++c2) {
-                    float a = fast_exp2(fmaf(s_[2 * c2], c_exp, nL2));
-                    float b = fast_exp2(fmaf(s_[2 * c2 + 1], c_exp, nL2));
+                    const float2 x = __ffma2_rn(make_float2(s_[2 * c2], s_[2 * c2 + 1]), cexp2, nm2);
+                    float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
                     if constexpr (!FULL) {
-                        a = ((vmask >> (2 * c2)) & 1u) ? a : 0.f;
-                        b = ((vmask >> (2 * c2 + 1)) & 1u) ? b : 0.f;
+                        pr.x = ((vmask >> (2 * c2)) & 1) ? pr.x : 0.f;
+                        pr.y = ((vmask >> (2 * c2 + 1)) & 1) ? pr.y : 0.f;
                     }
-                    run_sum += a + b;
-                    w0[c2] = pack2<BF16>(a, b);
+                    sum2 = __fadd2_rn(sum2, pr);
+                    w0[c2] = pack2<BF16>(pr.x, pr.y);
                 }
+                l_run += sum2.x + sum2.y;
+                BOB_PH(2)
+                // my group's previous product has consumed its operand and finished with the accumulator
                 if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
+                BOB_PH(3)
+                if (rescale) {
+                    tc_fence_after_sync();
+                    const uint32_t tacc = tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + grp * DPAD;
+                    #pragma unroll
+                    for (int ch = 0; ch < DPAD / 16; ++ch) {
+                        float t[16];
+                        uint32_t u[16];
+                        tmem_ld16(tacc + 16 * ch, t);
+                        tmem_wait_ld();
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) u[i] = __float_as_uint(t[i] * factor);
+                        tmem_st8(tacc + 16 * ch, u);
+                        tmem_st8(tacc + 16 * ch + 8, u + 8);
+                    }
+                }
                 #pragma unroll
                 for (int h = 0; h < CW / 16; ++h) tmem_st8(op_taddr + 8 * h, w0 + 8 * h);
+                ++n_op_item;
             } else {
                 // accumulator order: S, dP (first backward) or S, F, dP, C (second backward).
                 // My CW columns are taken in rounds of RW.  LOAD_ALL (second backward, 32 columns per
@@ -1001,33 +1016,30 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
 
         // ---- epilogue ------------------------------------------------------------------------
-        if constexpr (MODE == kFwd) {
-            if (total == 0 && grp == 0 && sp == 0 && own_ok) p.lse[row_stat] = -INFINITY;
-            if (total > 0 && !fwd_combined) {
-                red_buf[(grp * NSPLIT + sp) * 128 + row] = run_max;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_pw_all);
-                // a second arrival (below) must not land in this phase: wait until it has completed
-                if (ok) ok = pw_wait(bar_pw_all, pw_all_phase);
-            }
-            if (total > 0) pw_all_phase ^= 1u;       // first use of the all-groups barrier in this item
-        }
-        float fwd_inv_l = 0.f;                       // forward: 1 / (sum of the row's probabilities)
+        float fwd_k0 = 0.f, fwd_k1 = 0.f;            // forward: weights of the two groups' accumulators
         if constexpr (MODE == kFwd) {
             ok = __all_sync(0xffffffffu, ok);
-            if (ok && total > 0) {
-                // second use: every slice's sum of probabilities -> the row's normaliser and lse
-                constexpr int NPART = NG * NSPLIT;
-                red_buf[(NPART + grp * NSPLIT + sp) * 128 + row] = run_sum;
+            if (ok) {
+                // both groups' (reference, sum) of my row -> the row's normaliser and lse.  The
+                // exchange buffer alternates between items: a thread may start the next item while
+                // another still reads this one's values.
+                float* xb = red_buf + (n_items_done & 1) * (2 * NG * 128);
+                xb[grp * 128 + row] = m_ref;
+                xb[(NG + grp) * 128 + row] = l_run;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pw_all);
                 ok = pw_wait(bar_pw_all, pw_all_phase);
                 pw_all_phase ^= 1u;
-                float l = 0.f;
-                #pragma unroll
-                for (int k = 0; k < NPART; ++k) l += red_buf[(NPART + k) * 128 + row];
-                fwd_inv_l = (l > 0.f) ? 1.f / l : 0.f;
-                if (lse_writer && own_ok) p.lse[row_stat] = (l > 0.f) ? (log2f(l) - nL2) * kLn2 : -INFINITY;
+                const float m0 = xb[row], m1 = xb[128 + row];
+                const float m = fmaxf(m0, m1);
+                const float a0 = fast_exp2(m0 - m), a1 = fast_exp2(m1 - m);
+                const float l = a0 * xb[2 * 128 + row] + a1 * xb[3 * 128 + row];
+                const float inv = (l > 0.f) ? 1.f / l : 0.f;
+                // a group that took no tile of this item has never written its accumulator
+                const int first_grp = (cnt - total) % NG;
+                fwd_k0 = (total >= 2 || (total == 1 && first_grp == 0)) ? a0 * inv : 0.f;
+                fwd_k1 = (total >= 2 || (total == 1 && first_grp == 1)) ? a1 * inv : 0.f;
+                if (grp == 0 && own_ok) p.lse[row_stat] = (l > 0.f) ? (m + log2f(l)) * kLn2 : -INFINITY;
             }
         }
         float alpha = 0.f, ecirc = 0.f;
@@ -1067,7 +1079,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 const int col = (grp * NSPLIT + sp) * DC + 16 * ch;
                 if (total > 0 && col < p.D) {
                     tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 0 * DPAD + col, acc0[ch]);
-                    if constexpr (MT::NOUT > 1) tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 1 * DPAD + col, acc1[ch]);
+                    if constexpr (CFG::NACC > 1) tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 1 * DPAD + col, acc1[ch]);
                 } else {
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) { acc0[ch][i] = 0.f; acc1[ch][i] = 0.f; }
@@ -1091,7 +1103,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 if constexpr (!EARLY) {
                     if (total > 0) {
                         tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 0 * DPAD + col, late0);
-                        if constexpr (MT::NOUT > 1) tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 1 * DPAD + col, late1);
+                        if constexpr (CFG::NACC > 1) tmem_ld16(tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + 1 * DPAD + col, late1);
                         if (last) { release_outputs(); released = true; } else tmem_wait_ld();
                     } else {
                         #pragma unroll
@@ -1102,8 +1114,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 float* a1 = EARLY ? acc1[EARLY ? c / 16 : 0] : late1;
                 if (!own_ok) continue;          // stores are per row
                 if constexpr (MODE == kFwd) {
+                    // weighted sum of the two groups' accumulators (weight 0: never written, not read)
                     #pragma unroll
-                    for (int i = 0; i < 16; ++i) a0[i] *= fwd_inv_l;
+                    for (int i = 0; i < 16; ++i)
+                        a0[i] = (fwd_k0 != 0.f ? fwd_k0 * a0[i] : 0.f) + (fwd_k1 != 0.f ? fwd_k1 * a1[i] : 0.f);
                     store16_from_float<BF16>(p.res0, res_off + col, a0);
                 } else if constexpr (MODE == kBwd1Row) {
                     #pragma unroll
@@ -1194,6 +1208,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             }
         }
         if (total > 0) ++n_live;
+        ++n_items_done;
         BOB_PH(5)
         }   // items
         if constexpr (CFG::STAGED_IO) cp_async_wait_all();
