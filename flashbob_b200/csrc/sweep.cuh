@@ -149,6 +149,7 @@ struct SweepConfig {
     static constexpr int STAGE_ROOM = (232448 - FIXED_BYTES) / OTH_STAGE_BYTES;
     static constexpr int STAGE_MAX = 6;
     static constexpr int NSTAGE = STAGE_ROOM >= STAGE_MAX ? STAGE_MAX : (STAGE_ROOM >= 2 ? STAGE_ROOM : 2);
+    static_assert(NSTAGE > NG, "score products may run NG tiles ahead: they need NG + 1 stages of swept tiles");
     // shared memory map (offsets from a 1024-byte aligned base)
     static constexpr int OFF_OWN = 0;
     static constexpr int OFF_OTH = OFF_OWN + MT::NOWN * OWN_TILE_BYTES;
@@ -544,12 +545,31 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             if (total == 0) continue;
             ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
             if (!ok) give_up(kStatusTimeoutMma);
-            ok = ok && issue_scores(cnt, stage, round);
+            // Score products run LOOK tiles ahead of the output products.  With two pointwise groups a
+            // group's next scores are best issued as soon as it has read the current ones, while it
+            // still works on them (LOOK = 2, forward); otherwise one tile ahead.
+            constexpr int LOOK = (MODE == kFwd) ? NG : 1;
+            int sc_it = 0, sc_stage = stage, sc_round = round;     // next tile to issue scores for
+            (void)sc_it; (void)sc_stage; (void)sc_round;
+            auto scores_upto = [&](int last) {
+                while (ok && sc_it < total && sc_it <= last) {
+                    ok = issue_scores(cnt + sc_it, sc_stage, sc_round);
+                    ++sc_it;
+                    if (++sc_stage == NSTAGE) { sc_stage = 0; ++sc_round; }
+                }
+            };
+            if constexpr (LOOK == 1) ok = ok && issue_scores(cnt, stage, round);
+            else scores_upto(LOOK - 1);
             int n_out = 0;                            // output rounds of this item
             for (int it = 0; ok && it < total; ++it) {
                 int nstage = stage + 1, nround = round;
                 if (nstage == NSTAGE) { nstage = 0; ++nround; }
-                if (it + 1 < total && !issue_scores(cnt + it + 1, nstage, nround)) { ok = false; break; }
+                if constexpr (LOOK == 1) {
+                    if (it + 1 < total && !issue_scores(cnt + it + 1, nstage, nround)) { ok = false; break; }
+                } else {
+                    scores_upto(it + LOOK);
+                    if (!ok) break;
+                }
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
                 const bool has_out = true;
                 if (has_out) {
