@@ -111,7 +111,8 @@ struct SweepConfig {
     // Second backward with 32 columns per pointwise thread: the two pointwise warpgroups take
     // registers over from the warpgroup of the MMA and TMA warps (padded to four warps, two of them
     // idle) once the kernel runs, which lets a pointwise thread hold a whole tile's score columns.
-    static constexpr bool REBALANCE = (MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32 && NG == 1 && NPW == 256;
+    static constexpr bool REBALANCE = NG == 1 && NPW == 256 &&
+        (((MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32) || ((MODE == kBwd1Row || MODE == kBwd1Col) && CW == 64));
     static constexpr int NTHREADS = REBALANCE ? 384 : NPW + 64;   // + MMA warp + TMA warp (+ 2 idle warps)
 #ifndef BOB_REGS_POINTWISE
 #define BOB_REGS_POINTWISE 224
@@ -221,7 +222,7 @@ template <int MODE, int DPAD, int TN, bool BF16, int NG, int CW>
 __global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN, NG, CW>::NTHREADS, 1)
 sweep_kernel(const __grid_constant__ SweepParams p) {
     using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
-    static_assert(CW == 16 || CW == 32 || (CW == 64 && MODE == kFwd), "16 or 32 columns per pointwise thread (forward: 64)");
+    static_assert(CW == 16 || CW == 32 || (CW == 64 && MODE <= kBwd1Col), "16 or 32 columns per pointwise thread (forward, first backward: 64)");
     constexpr int RW = 16;                     // columns per round of tensor-memory loads
     using MT = ModeTraits<MODE>;
     constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, GP = CFG::GP, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
@@ -785,10 +786,11 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_sc_empty(grp));
                 // largest unmasked score of my row in this tile (the scale is positive)
-                float mr = -3.0e38f;
+                float mr4[4] = {-3.0e38f, -3.0e38f, -3.0e38f, -3.0e38f};     // four chains, for instruction-level parallelism
                 #pragma unroll
                 for (int c = 0; c < CW; ++c)
-                    mr = fmaxf(mr, (FULL || ((vmask >> c) & 1)) ? s_[c] : -3.0e38f);
+                    mr4[c & 3] = fmaxf(mr4[c & 3], (FULL || ((vmask >> c) & 1)) ? s_[c] : -3.0e38f);
+                const float mr = fmaxf(fmaxf(mr4[0], mr4[1]), fmaxf(mr4[2], mr4[3]));
                 const float mt = fmaxf(mr * c_exp, -1e30f);
                 // move the reference only when the maximum has outgrown it; the whole warp then
                 // rescales its rows of the output accumulator (factor 1 where nothing changed)
@@ -799,7 +801,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 l_run *= factor;
                 const float nm = -m_ref;
                 uint32_t w0[CW / 2];
-                float2 sum2 = make_float2(0.f, 0.f);
+                float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
                 const float2 cexp2 = make_float2(c_exp, c_exp), nm2 = make_float2(nm, nm);
                 #pragma unroll
                 for (int c2 = 0; c2 < CW / 2; ++c2) {
@@ -809,10 +811,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         pr.x = ((vmask >> (2 * c2)) & 1) ? pr.x : 0.f;
                         pr.y = ((vmask >> (2 * c2 + 1)) & 1) ? pr.y : 0.f;
                     }
-                    sum2 = __fadd2_rn(sum2, pr);
+                    sum4[c2 & 3] = __fadd2_rn(sum4[c2 & 3], pr);
                     w0[c2] = pack2<BF16>(pr.x, pr.y);
                 }
-                l_run += sum2.x + sum2.y;
+                {
+                    const float2 t = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
+                    l_run += t.x + t.y;
+                }
                 BOB_PH(2)
                 // my group's previous product has consumed its operand and finished with the accumulator
                 if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
@@ -844,7 +849,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 // the accumulators are handed back when the last round has been loaded.  Each round's
                 // packed operands go to tensor memory as soon as they are formed.
                 constexpr int R = CW / RW;
-                constexpr bool LOAD_ALL = BWD2 && CW == 32;
+                constexpr bool LOAD_ALL = CFG::REBALANCE;
                 constexpr int NB = LOAD_ALL ? R : 1;
                 const float2 cexp2 = make_float2(c_exp, c_exp);
                 const float2 scale2 = make_float2(p.scale, p.scale);
