@@ -111,8 +111,10 @@ struct SweepConfig {
     // Second backward with 32 columns per pointwise thread: the two pointwise warpgroups take
     // registers over from the warpgroup of the MMA and TMA warps (padded to four warps, two of them
     // idle) once the kernel runs, which lets a pointwise thread hold a whole tile's score columns.
-    static constexpr bool REBALANCE = NG == 1 && NPW == 256 &&
-        (((MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32) || ((MODE == kBwd1Row || MODE == kBwd1Col) && CW == 64));
+    static constexpr bool REBALANCE = NPW == 256 &&
+        ((NG == 1 && (MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32) ||
+         (NG == 1 && (MODE == kBwd1Row || MODE == kBwd1Col) && CW == 64) ||
+         (NG == 2 && MODE == kFwd && CW == 128));
     static constexpr int NTHREADS = REBALANCE ? 384 : NPW + 64;   // + MMA warp + TMA warp (+ 2 idle warps)
 #ifndef BOB_REGS_POINTWISE
 #define BOB_REGS_POINTWISE 224
@@ -132,7 +134,7 @@ struct SweepConfig {
     // The forward keeps one output accumulator per pointwise group (each group runs its own online
     // softmax over the tiles it takes; the epilogue merges them).
     static constexpr int NACC = (MODE == kFwd) ? NG : MT::NOUT;
-    static_assert(MODE != kFwd || (NG == 2 && CW == TN), "forward: two groups, one thread per row");
+    static_assert(MODE != kFwd || (NG == 2 && CW == TN && (TN == 64 || TN == 128)), "forward: two groups, one thread per row");
     static constexpr int OUT_COLS = NACC * DPAD;
     static constexpr int TMEM_NEED = NG * (SC_COLS + OPER_COLS) + OUT_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
@@ -222,7 +224,8 @@ template <int MODE, int DPAD, int TN, bool BF16, int NG, int CW>
 __global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN, NG, CW>::NTHREADS, 1)
 sweep_kernel(const __grid_constant__ SweepParams p) {
     using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
-    static_assert(CW == 16 || CW == 32 || (CW == 64 && MODE <= kBwd1Col), "16 or 32 columns per pointwise thread (forward, first backward: 64)");
+    static_assert(CW == 16 || CW == 32 || (CW == 64 && MODE <= kBwd1Col) || (CW == 128 && MODE == kFwd),
+                  "16 or 32 columns per pointwise thread (first backward: also 64; forward: 64 or 128)");
     constexpr int RW = 16;                     // columns per round of tensor-memory loads
     using MT = ModeTraits<MODE>;
     constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, GP = CFG::GP, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
@@ -756,11 +759,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             // ---- which of my 16 columns are unmasked: bits [mlo, mhi] of vmask ----------------
             // dist = query position - key position; unmasked iff in range and, when causal,
             // 0 <= dist (< window)
+            // Up to 64 columns per thread: a bit mask; more (forward, 128): the range itself.
             using mask_t = typename std::conditional<(CW > 32), unsigned long long, uint32_t>::type;
-            constexpr mask_t kAllCols = (CW == 64) ? ~mask_t(0) : ((CW == 32) ? mask_t(0xFFFFFFFFu) : mask_t(0xFFFFu));
+            constexpr mask_t kAllCols = (CW >= 64) ? ~mask_t(0) : ((CW == 32) ? mask_t(0xFFFFFFFFu) : mask_t(0xFFFFu));
             mask_t vmask = kAllCols;
+            int mlo = 0, mhi = CW - 1;
             if constexpr (!FULL) {
-                int mlo = 0, mhi = min(CW - 1, n_oth - (oth0 + col0) - 1);
+                mhi = min(CW - 1, n_oth - (oth0 + col0) - 1);
                 if (causal) {
                     if constexpr (!COL) {
                         const int d0 = own_idx + doff - (oth0 + col0);       // dist falls with the column
@@ -772,8 +777,16 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         if (window > 0) mhi = min(mhi, window - 1 - d0);
                     }
                 }
-                vmask = (own_ok && mhi >= mlo) ? ((kAllCols >> (CW - 1 - mhi)) & (kAllCols << mlo)) : mask_t(0);
+                if (!own_ok) { mlo = 1; mhi = 0; }
+                if constexpr (CW <= 64)
+                    vmask = (mhi >= mlo) ? ((kAllCols >> (CW - 1 - mhi)) & (kAllCols << mlo)) : mask_t(0);
             }
+            auto valid = [&](int c) -> bool {        // column c of mine is unmasked (c is a constant after unrolling)
+                if constexpr (FULL) return true;
+                else if constexpr (CW <= 64) return ((vmask >> c) & 1) != 0;
+                else return c >= mlo && c <= mhi;
+            };
+            (void)valid; (void)vmask;
 
             if constexpr (MODE == kFwd) {
                 // One thread owns a whole row of the tile.
@@ -789,7 +802,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 float mr4[4] = {-3.0e38f, -3.0e38f, -3.0e38f, -3.0e38f};     // four chains, for instruction-level parallelism
                 #pragma unroll
                 for (int c = 0; c < CW; ++c)
-                    mr4[c & 3] = fmaxf(mr4[c & 3], (FULL || ((vmask >> c) & 1)) ? s_[c] : -3.0e38f);
+                    mr4[c & 3] = fmaxf(mr4[c & 3], valid(c) ? s_[c] : -3.0e38f);
                 const float mr = fmaxf(fmaxf(mr4[0], mr4[1]), fmaxf(mr4[2], mr4[3]));
                 const float mt = fmaxf(mr * c_exp, -1e30f);
                 // move the reference only when the maximum has outgrown it; the whole warp then
@@ -799,30 +812,18 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 float factor = 1.f;
                 if (grow) { factor = fast_exp2(m_ref - mt); m_ref = mt; }
                 l_run *= factor;
-                const float nm = -m_ref;
-                uint32_t w0[CW / 2];
-                float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-                const float2 cexp2 = make_float2(c_exp, c_exp), nm2 = make_float2(nm, nm);
-                #pragma unroll
-                for (int c2 = 0; c2 < CW / 2; ++c2) {
-                    const float2 x = __ffma2_rn(make_float2(s_[2 * c2], s_[2 * c2 + 1]), cexp2, nm2);
-                    float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-                    if constexpr (!FULL) {
-                        pr.x = ((vmask >> (2 * c2)) & 1) ? pr.x : 0.f;
-                        pr.y = ((vmask >> (2 * c2 + 1)) & 1) ? pr.y : 0.f;
-                    }
-                    sum4[c2 & 3] = __fadd2_rn(sum4[c2 & 3], pr);
-                    w0[c2] = pack2<BF16>(pr.x, pr.y);
-                }
-                {
-                    const float2 t = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
-                    l_run += t.x + t.y;
-                }
                 BOB_PH(2)
-                // my group's previous product has consumed its operand and finished with the accumulator
-                if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
+                // My group's previous product must have consumed its operand and finished with the
+                // accumulator before I touch either.  With 128 columns the probabilities go to tensor
+                // memory 16 at a time (registers), so the wait comes first; with 64 they are all
+                // formed before the wait.
+                constexpr bool WAIT_FIRST = CW > 64;
+                uint32_t wall[WAIT_FIRST ? 1 : CW / 2];
+                if constexpr (WAIT_FIRST) {
+                    if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
+                }
                 BOB_PH(3)
-                if (rescale) {
+                auto rescale_rows = [&]() {
                     tc_fence_after_sync();
                     const uint32_t tacc = tlane + NG * (CFG::SC_COLS + CFG::OPER_COLS) + grp * DPAD;
                     #pragma unroll
@@ -836,9 +837,40 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         tmem_st8(tacc + 16 * ch, u);
                         tmem_st8(tacc + 16 * ch + 8, u + 8);
                     }
-                }
+                };
+                if (WAIT_FIRST && rescale) rescale_rows();
+                // probabilities relative to the reference, 16 columns at a time straight into tensor memory
+                const float nm = -m_ref;
+                float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+                const float2 cexp2 = make_float2(c_exp, c_exp), nm2 = make_float2(nm, nm);
                 #pragma unroll
-                for (int h = 0; h < CW / 16; ++h) tmem_st8(op_taddr + 8 * h, w0 + 8 * h);
+                for (int h = 0; h < CW / 16; ++h) {
+                    uint32_t w0[8];
+                    #pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int c = 16 * h + 2 * k;
+                        const float2 x = __ffma2_rn(make_float2(s_[c], s_[c + 1]), cexp2, nm2);
+                        float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                        if constexpr (!FULL) {
+                            pr.x = valid(c) ? pr.x : 0.f;
+                            pr.y = valid(c + 1) ? pr.y : 0.f;
+                        }
+                        sum4[k & 3] = __fadd2_rn(sum4[k & 3], pr);
+                        w0[k] = pack2<BF16>(pr.x, pr.y);
+                        if constexpr (!WAIT_FIRST) wall[8 * h + k] = w0[k];
+                    }
+                    if constexpr (WAIT_FIRST) tmem_st8(op_taddr + 8 * h, w0);
+                }
+                {
+                    const float2 t = __fadd2_rn(__fadd2_rn(sum4[0], sum4[1]), __fadd2_rn(sum4[2], sum4[3]));
+                    l_run += t.x + t.y;
+                }
+                if constexpr (!WAIT_FIRST) {
+                    if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
+                    if (rescale) rescale_rows();
+                    #pragma unroll
+                    for (int h = 0; h < CW / 16; ++h) tmem_st8(op_taddr + 8 * h, wall + 8 * h);
+                }
                 ++n_op_item;
             } else {
                 // accumulator order: S, dP (first backward) or S, F, dP, C (second backward).
