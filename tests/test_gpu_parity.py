@@ -128,6 +128,35 @@ def test_all_eight_outputs_match_oracle(name):
         _check(f"{name}:{n}", got[n], getattr(ref, n), dtype)
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("D", [64, 128])
+def test_forward_when_the_row_maximum_keeps_growing(causal, D):
+    """Scores that grow along the keys by ~14 (log2 units) per 128 keys: every tile raises the running
+    maximum past the forward's rescaling threshold, so the accumulator in tensor memory is rescaled
+    tile after tile and the two pointwise groups end with very different references."""
+    B, H, N = 1, 2, 640
+    g = torch.Generator().manual_seed(5)
+    q = 0.05 * torch.randn(B, H, N, D, generator=g)
+    k = 0.05 * torch.randn(B, H, N, D, generator=g)
+    q[..., 0] = 4.0
+    k[..., 0] = 0.15 * torch.arange(N, dtype=torch.float32) * (8.0 / D ** 0.5) ** -1 * 1.0
+    v = torch.randn(B, H, N, D, generator=g)
+    dO, uQ, uK, uV = (torch.randn(B, H, N, D, generator=g) for _ in range(4))
+    q, k, v, dO, uQ, uK, uV = (t.to(BF16) for t in (q, k, v, dO, uQ, uK, uV))
+    geom = _geom(N, N, is_causal=causal)
+    ref = O.bob_closed_form(q, k, v, dO, uQ, uK, uV, **geom)
+    got, lse, _ = _run_kernels(q, k, v, dO, uQ, uK, uV, geom)
+    # the maximum really moves: the lse of late rows is far above that of early rows
+    assert (ref.lse[..., -1] - ref.lse[..., 0]).min().item() > 20.0 or not causal
+    torch.testing.assert_close(lse.cpu().double(), ref.lse, rtol=1e-5, atol=2e-5)
+    # out and dV (= P^T dO) are free of cancellation; with keys this large the other gradients are
+    # differences of big rounded terms and say nothing about the forward
+    for n in ("out", "dV"):
+        _check(f"growing:{n}", got[n], getattr(ref, n), BF16)
+    for n in O.OUTPUT_NAMES:
+        assert torch.isfinite(got[n].float()).all(), n
+
+
 @pytest.mark.parametrize("missing", [("k", "v"), ("q",), ("q", "k"), ("v",), ("q", "v")])
 def test_undefined_tangents(missing):
     """Undefined tangents switch products off; results equal the oracle with those tangents zero
