@@ -56,7 +56,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one second-backward launch pair, from the ncu capture
 # summarised in profiles/bwd2_kernels_gqa_s4096_d64.md: that capture ran a quarter of the c2 workload
 # (8 of 32 query heads; traffic grows with the head count), so its 51.3 MB is scaled by 4.
-TRAFFIC_BYTES = {"c2": 4 * (33_884_416 + 1_792 + 17_369_088)}
+TRAFFIC_BYTES = {"c2": 4 * (33_890_560 + 8_960 + 17_369_088)}
 TRAFFIC_NOTE = "ncu dram bytes of the row-owned + column-owned kernels on a quarter-size capture, x4; c2 only"
 
 
