@@ -133,7 +133,7 @@ static int dispatch(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* 
     if (g->D <= 64) {
         if constexpr (kSecond)           return launch_sweep<MODE, 64, 64, BF16, 1, 32>(g, prm, tensors, stream);
         else if constexpr (MODE == kFwd) return launch_sweep<MODE, 64, 128, BF16, 2, 128>(g, prm, tensors, stream);
-        else                             return launch_sweep<MODE, 64, 128, BF16, 1, 64>(g, prm, tensors, stream);
+        else                             return launch_sweep<MODE, 64, 128, BF16, 1, 32>(g, prm, tensors, stream);
     }
     if constexpr (kSecond)           return launch_sweep<MODE, 128, 32, BF16>(g, prm, tensors, stream);
     else if constexpr (MODE == kFwd) return launch_sweep<MODE, 128, 64, BF16, 2, 64>(g, prm, tensors, stream);

@@ -724,8 +724,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             const uint16_t* g_out = static_cast<const uint16_t*>(p.out) + (long long)batch * p.out_sb + (long long)head * p.out_sh + (long long)own0 * p.out_sn;
             const uint16_t* g_dq = static_cast<const uint16_t*>(p.dQ) + (long long)batch * p.dQ_sb + (long long)head * p.dQ_sh + (long long)own0 * p.dQ_sn;
             #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int id = tid + 256 * k, r = id >> 3, c = id & 7;
+            for (int k = 0; k < 1024 / NPW; ++k) {
+                const int id = tid + NPW * k, r = id >> 3, c = id & 7;
                 if (own0 + r < n_own && c * 8 < p.D) {
                     const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
                     cp_async16(io_out + off, g_out + (long long)r * p.out_sn + c * 8);
@@ -733,8 +733,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 }
             }
             #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int id = tid + 256 * k, r = id >> 4, c = id & 15;
+            for (int k = 0; k < 2048 / NPW; ++k) {
+                const int id = tid + NPW * k, r = id >> 4, c = id & 15;
                 if (own0 + r < n_own && c * 4 < p.D)
                     cp_async16(io_pk + r * 256 + ((c & 8) << 4) + (((c ^ r) & 7) << 4), p.pk + (tile_row0 + r) * p.D + c * 4);
             }
@@ -1253,8 +1253,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 uint16_t* g_q = static_cast<uint16_t*>(p.res0) + tile_row0 * p.D;
                 uint16_t* g_do = static_cast<uint16_t*>(p.res1) + tile_row0 * p.D;
                 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int id = tid + 256 * k, r = id >> 3, c = id & 7;
+                for (int k = 0; k < 1024 / NPW; ++k) {
+                    const int id = tid + NPW * k, r = id >> 3, c = id & 7;
                     if (own0 + r < n_own && c * 8 < p.D) {
                         const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
                         *reinterpret_cast<uint4*>(g_q + (long long)r * p.D + c * 8) = ld_shared_v4(io_dq + off);
