@@ -16,7 +16,8 @@ FLOP convention (algorithmic, matmul only): A = attending (query, key) pairs per
 u = 2*A*D*B*Hq; the second backward is 12 u (no credit for recomputation).
 
 Output: one JSON line on rank 0.  `value` = whole-job TFLOP/s with inputs resident in HBM;
-`e2e` = the same through the C-ABI call with pinned host buffers (copies inside the timed region);
+`e2e` = the same through the C-ABI calls with pinned host buffers holding the reference-level inputs
+of the second backward (copies inside the timed region; delta and pk are regenerated on the device);
 `roofline` = tensor roofline of the two-kernel second backward; `cpu_baseline` = the CPU port of
 the reference's math route timed on a bounded sample.  `--impl reference` times that CPU port
 alone (rank 0), as the reference arm.
@@ -307,9 +308,19 @@ def main():
     os.environ.pop("BOB_SM100_BWD2_KERNELS", None)
 
     # ---- end to end: pinned host buffers -> device -> C-ABI call -> pinned host results --------
-    names_in = ("q", "k", "v", "out", "lse", "delta", "pk", "dO", "dQ", "uQ", "uK", "uV")
+    # The host holds what the reference's second backward is called with (src/bob/sdpa.py:175-236:
+    # q, k, v, out, lse, dO, dQ and the three tangents).  delta and pk are this library's own
+    # by-products of the first backward; they never leave the device and are regenerated there each
+    # step by bob_sm100_bwd1 (inside the timed region), which is cheaper than carrying 34 MB of
+    # fp32 pk over PCIe.
+    names_in = ("q", "k", "v", "out", "lse", "dO", "dQ", "uQ", "uK", "uV")
+    names_dev = names_in + ("delta", "pk", "dQ1", "dK1", "dV1")
+    d["dQ1"], d["dK1"], d["dV1"] = torch.empty_like(d["dQ"]), torch.empty_like(d["k"]), torch.empty_like(d["v"])
     pin = {n: d[n].cpu().pin_memory() for n in names_in}
-    stage = {n: torch.empty_like(d[n]) for n in names_in}
+    stage = {n: torch.empty_like(d[n]) for n in names_dev}
+    ws_e2e = torch.empty(max(lib.bob_sm100_workspace_bytes(_lib.STAGE_BWD1, ctypes.byref(g)),
+                             lib.bob_sm100_workspace_bytes(_lib.STAGE_BWD2, ctypes.byref(g))),
+                         dtype=torch.uint8, device=dev)
     pin_out = {n: torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for n, t in res.items()}
     h2d = sum(t.numel() * t.element_size() for t in pin.values())
     d2h = sum(t.numel() * t.element_size() for t in pin_out.values())
@@ -318,15 +329,19 @@ def main():
     # step i+1's inputs cross PCIe and step i-1's results go back.  Every step still copies all of
     # its inputs from pinned host memory and all of its results back to pinned host memory.
     s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    stage2 = [stage, {n: torch.empty_like(d[n]) for n in names_in}]
+    stage2 = [stage, {n: torch.empty_like(d[n]) for n in names_dev}]
     res2 = [res, {n: torch.empty_like(t) for n, t in res.items()}]
     pin_out2 = [pin_out, {n: torch.empty(t.shape, dtype=t.dtype, device="cpu").pin_memory() for n, t in res.items()}]
 
     def bwd2_on(src, dst, cuda_stream):
+        rc = lib.bob_sm100_bwd1(ctypes.byref(g), vp(src["q"]), vp(src["k"]), vp(src["v"]), vp(src["out"]),
+                                vp(src["lse"]), vp(src["dO"]), vp(src["dQ1"]), vp(src["dK1"]), vp(src["dV1"]),
+                                vp(src["delta"]), vp(src["pk"]), vp(ws_e2e), ctypes.c_void_p(cuda_stream))
+        _lib.check(rc, "bob_sm100_bwd1")
         rc = lib.bob_sm100_bwd2(ctypes.byref(g), vp(src["q"]), vp(src["k"]), vp(src["v"]), vp(src["out"]),
                                 vp(src["lse"]), vp(src["delta"]), vp(src["pk"]), vp(src["dO"]), vp(src["dQ"]),
                                 vp(src["uQ"]), vp(src["uK"]), vp(src["uV"]), vp(dst["Qbar"]), vp(dst["Kbar"]),
-                                vp(dst["Vbar"]), vp(dst["dObar"]), vp(ws), ctypes.c_void_p(cuda_stream))
+                                vp(dst["Vbar"]), vp(dst["dObar"]), vp(ws_e2e), ctypes.c_void_p(cuda_stream))
         _lib.check(rc, "bob_sm100_bwd2")
 
     def e2e_run(n_steps):
@@ -413,8 +428,11 @@ def main():
                      "kernel_ms": kernel_ms},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "ms_per_step": e2e_ms.item() / e2e_steps,
-                "how": "pinned host -> device -> bob_sm100_bwd2 -> pinned host every step; steps pipelined "
-                       "over copy-in / compute / copy-out streams; inputs per step exceed L2"},
+                "how": "pinned host (q,k,v,out,lse,dO,dQ,uQ,uK,uV) -> device -> bob_sm100_bwd1 (delta, pk) + "
+                       "bob_sm100_bwd2 -> pinned host (Qbar,Kbar,Vbar,dObar) every step; steps pipelined over "
+                       "copy-in / compute / copy-out streams; inputs per step exceed L2",
+                "gpu_launches_per_step": lib.bob_sm100_kernel_launches(_lib.STAGE_BWD1, ctypes.byref(g)) +
+                                         lib.bob_sm100_kernel_launches(_lib.STAGE_BWD2, ctypes.byref(g))},
         "gpu_launches": lib.bob_sm100_kernel_launches(_lib.STAGE_BWD2, ctypes.byref(g)) * args.steps,
         "clocks": clocks,
         "wall_s_timed_region": wall,
