@@ -685,29 +685,30 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         (void)m_ref; (void)l_run; (void)n_op_item;
 
         if constexpr (MODE == kBwd1Row) {
-            // delta = rowsum(dO * out), each slice sums its share of the head dim
-            float part = 0.f;
-            if (own_ok) {
-                constexpr int DC = DPAD / NSPLIT;
-                const long long o_off = (long long)batch * p.out_sb + (long long)head * p.out_sh + (long long)own_idx * p.out_sn;
-                const long long g_off = (long long)batch * p.dO_sb + (long long)head * p.dO_sh + (long long)own_idx * p.dO_sn;
-                #pragma unroll
-                for (int c = 0; c < DC; c += 16) {
-                    const int col = sp * DC + c;
-                    if (col < p.D) {
-                        float a[16], b[16];
-                        load16_as_float<BF16>(p.out, o_off + col, a);
-                        load16_as_float<BF16>(p.dO, g_off + col, b);
-                        #pragma unroll
-                        for (int i = 0; i < 16; ++i) part = fmaf(a[i], b[i], part);
-                    }
-                }
-            }
-            red_buf[sp * 128 + row] = part;
-            ok = pw_sync();
-            float dlt = 0.f;
+            // delta = rowsum(dO * out).  The tile's rows are read cooperatively, 16 bytes per thread with
+            // the lanes of a row next to each other (whole 128-byte lines per request), each thread sums
+            // its eight products and the lanes of a row combine by shuffles.
+            static_assert(NG == 1, "the cooperative delta uses the single group's barrier");
+            constexpr int CH = DPAD / 8;                 // 16-byte chunks per row
+            const uint16_t* g_out = static_cast<const uint16_t*>(p.out) + (long long)batch * p.out_sb + (long long)head * p.out_sh + (long long)own0 * p.out_sn;
+            const uint16_t* g_do = static_cast<const uint16_t*>(p.dO) + (long long)batch * p.dO_sb + (long long)head * p.dO_sh + (long long)own0 * p.dO_sn;
             #pragma unroll
-            for (int k = 0; k < NSPLIT; ++k) dlt += red_buf[k * 128 + row];
+            for (int k = 0; k < 128 * CH / NPW; ++k) {
+                const int id = tid + NPW * k, r = id / CH, c = id % CH;
+                float part = 0.f;
+                if (own0 + r < n_own && c * 8 < p.D) {
+                    float a[8], b[8];
+                    unpack8_as_float<BF16>(*reinterpret_cast<const uint4*>(g_out + (long long)r * p.out_sn + c * 8), a);
+                    unpack8_as_float<BF16>(*reinterpret_cast<const uint4*>(g_do + (long long)r * p.dO_sn + c * 8), b);
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i) part = fmaf(a[i], b[i], part);
+                }
+                #pragma unroll
+                for (int m = CH / 2; m >= 1; m >>= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
+                if (c == 0) red_buf[r] = part;
+            }
+            ok = pw_sync();
+            const float dlt = red_buf[row];
             ok = ok && pw_sync();
             if (grp == 0 && sp == 0 && own_ok) p.delta[row_stat] = dlt;
             ndlt = -dlt;
