@@ -120,12 +120,15 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
     return cudaGetLastError() == cudaSuccess ? 0 : kErrLaunch;
 }
 
-// Tile table.  Head dim <= 64: 64-wide swept tiles and 32 columns per pointwise thread everywhere.
-// Forward and first backward need few accumulators, so tensor memory holds two sets of them and two
-// pointwise groups (2 x 256 threads) take the swept tiles in turn; the second backward has one group
-// of 256 threads with 168 registers each.  Head dim
-// 128: 64-wide tiles except the second backward, whose four score accumulators and three or four
-// operands leave tensor memory (512 columns) room for 32-wide tiles only.
+// Tile table (template arguments: head dim, swept-tile width, dtype, pointwise groups, score columns
+// per pointwise thread).
+// Head dim <= 64.  Forward: 128-wide tiles, two groups of 128 threads, each thread a whole row, each
+// group its own online softmax and output accumulator.  First backward: 128-wide tiles, one group of
+// 512 threads (more warps per scheduler measured better than fewer threads holding more columns).
+// Second backward: four score accumulators, four operands and two outputs fill tensor memory at
+// 64-wide tiles; one group of 256 threads holds a whole tile's columns at 224 registers.
+// Head dim 128.  Forward: 64-wide tiles, two groups, a row per thread.  First backward: 64-wide tiles.
+// Second backward: tensor memory (512 columns) leaves room for 32-wide tiles only.
 template <int MODE, bool BF16>
 static int dispatch(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
                     cudaStream_t stream) {
