@@ -101,16 +101,17 @@ struct SweepConfig {
     using MT = ModeTraits<MODE>;
     // NG pointwise groups take the swept tiles in turn (group g: tiles g, g + NG, ...), each with its
     // own score accumulators and operand columns, so that one group's tensor-memory latencies hide
-    // behind the other group's arithmetic and the MMA warp always has a tile to work on.
-    // CW score columns per pointwise thread: 16 (more threads, 96 registers each) or 32 (half the
-    // threads with 168 registers each, enough to keep the next tensor-memory loads in flight while
-    // the current columns are computed)
+    // behind the other group's arithmetic and the MMA warp always has a tile to work on (forward:
+    // each group also has its own output accumulator).
+    // CW score columns per pointwise thread: 16 or 32 (more threads, at most 112 registers each),
+    // or, with registers taken over from the MMA / TMA warpgroup (REBALANCE), 32, 64 or 128 held at
+    // once by 256 threads.
     static constexpr int NSPLIT = TN / CW;
     static constexpr int GP = 128 * NSPLIT;                // pointwise threads per group
     static constexpr int NPW = GP * NG;                    // pointwise threads
-    // Second backward with 32 columns per pointwise thread: the two pointwise warpgroups take
-    // registers over from the warpgroup of the MMA and TMA warps (padded to four warps, two of them
-    // idle) once the kernel runs, which lets a pointwise thread hold a whole tile's score columns.
+    // Configurations with 256 pointwise threads that hold a whole tile's score columns: the two
+    // pointwise warpgroups take registers over from the warpgroup of the MMA and TMA warps (padded
+    // to four warps, two of them idle) once the kernel runs.
     static constexpr bool REBALANCE = NPW == 256 &&
         ((NG == 1 && (MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32) ||
          (NG == 1 && (MODE == kBwd1Row || MODE == kBwd1Col) && CW == 64) ||
