@@ -307,6 +307,28 @@ def main():
         kernel_ms[which] = sum(kms) / len(kms)
     os.environ.pop("BOB_SM100_BWD2_KERNELS", None)
 
+    # ---- the other two stages of the path, same geometry, same timing rules (secondary numbers) ---
+    sc = {n: torch.empty_like(d[s_]) for n, s_ in (("out", "q"), ("dQ", "q"), ("dK", "k"), ("dV", "k"))}
+    sc["lse"], sc["delta"], sc["pk"] = torch.empty_like(d["lse"]), torch.empty_like(d["delta"]), torch.empty_like(d["pk"])
+    ws1 = torch.empty(max(lib.bob_sm100_workspace_bytes(_lib.STAGE_FWD, ctypes.byref(g)),
+                          lib.bob_sm100_workspace_bytes(_lib.STAGE_BWD1, ctypes.byref(g))), dtype=torch.uint8, device=dev)
+    sp = ctypes.c_void_p(stream.cuda_stream)
+
+    def fwd_call():
+        _lib.check(lib.bob_sm100_fwd(ctypes.byref(g), vp(d["q"]), vp(d["k"]), vp(d["v"]), vp(sc["out"]),
+                                     vp(sc["lse"]), vp(ws1), sp), "bob_sm100_fwd")
+
+    def bwd1_call():
+        _lib.check(lib.bob_sm100_bwd1(ctypes.byref(g), vp(d["q"]), vp(d["k"]), vp(d["v"]), vp(d["out"]),
+                                      vp(d["lse"]), vp(d["dO"]), vp(sc["dQ"]), vp(sc["dK"]), vp(sc["dV"]),
+                                      vp(sc["delta"]), vp(sc["pk"]), vp(ws1), sp), "bob_sm100_bwd1")
+
+    stage_ms = {}
+    for name, fn, mult in (("forward", fwd_call, 2), ("first_backward", bwd1_call, 5)):
+        sms_, _ = timed_steps(fn, 2, min(args.steps, 10))
+        t = sum(sms_) / len(sms_)
+        stage_ms[name] = {"ms": t, "tflops": mult * unit_flops * B * Hq / (t * 1e-3) / 1e12}
+
     # ---- end to end: pinned host buffers -> device -> C-ABI call -> pinned host results --------
     # The host holds what the reference's second backward is called with (src/bob/sdpa.py:175-236:
     # q, k, v, out, lse, dO, dQ and the three tangents).  delta and pk are this library's own
@@ -426,6 +448,7 @@ def main():
                      "peak_source": peak_src,
                      "kernel": "second backward = row-owned kernel + column-owned kernel",
                      "kernel_ms": kernel_ms},
+        "other_stages": stage_ms,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "ms_per_step": e2e_ms.item() / e2e_steps,
                 "how": "pinned host (q,k,v,out,lse,dO,dQ,uQ,uK,uV) -> device -> bob_sm100_bwd1 (delta, pk) + "
