@@ -44,10 +44,13 @@ SYMBOLS = {
     "bob_sm100_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.POINTER(Geom)]),
     "bob_sm100_kernel_launches": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(Geom)]),
     "bob_sm100_read_status": (ctypes.c_int, [_vp, _vp]),
+    "bob_sm100_last_status": (ctypes.c_int, [ctypes.c_int]),
     "bob_sm100_fwd": (ctypes.c_int, [ctypes.POINTER(Geom)] + [_vp] * 7),
     "bob_sm100_bwd1": (ctypes.c_int, [ctypes.POINTER(Geom)] + [_vp] * 13),
     "bob_sm100_bwd2": (ctypes.c_int, [ctypes.POINTER(Geom)] + [_vp] * 18),
+    "bob_sm100_bwd2_part": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(Geom)] + [_vp] * 18),
     "bob_sm100_noalloc_max_rows": (ctypes.c_size_t, []),
+    "bob_sm100_noalloc_read_status": (ctypes.c_int, [ctypes.c_int, _vp]),
     "bob_sm100_bwd2_noalloc": (ctypes.c_int, [ctypes.POINTER(Geom)] + [_vp] * 17),
     "bob_sm100_timeout_selftest": (ctypes.c_int, [_vp, _vp]),
     "bob_sm100_selftest": (ctypes.c_int, [_vp, _vp, ctypes.c_int, _vp, _vp, _vp]),

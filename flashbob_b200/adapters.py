@@ -32,14 +32,19 @@ def hf_attention_interface(module, query, key, value, attention_mask=None, *, sc
                            is_causal=None, sliding_window=None, **_unused):
     """Hugging Face `AttentionInterface` signature: [B, H, N, D] tensors in, ([B, N, H, D], None) out.
 
-    Only implicit causal masking is supported (an explicit `attention_mask` must be None or purely
-    causal and is ignored); dropout must be 0.
+    Masking is implicit only: causal with right alignment (a decode step with one query and a cache
+    of N keys sees all of them), optionally limited to the last `sliding_window` keys.  An explicit
+    `attention_mask` is refused, as the reference's entry point does
+    (reference: examples/huggingface_backend.py:45-49): the operator takes no bias, so a padded
+    batch would silently attend to pad tokens.  Dropout must be 0.
     """
+    if attention_mask is not None:
+        raise NotImplementedError(
+            "sdpa_bob takes no attention bias, so padded batches are unsupported; "
+            "pass attention_mask=None with an unpadded causal batch")
     if dropout:
         raise NotImplementedError("attention dropout is not supported")
     causal = bool(getattr(module, "is_causal", True)) if is_causal is None else bool(is_causal)
-    if query.shape[2] == 1:
-        causal = False          # a single new token attends to the whole cache
-    out = sdpa_bob(query, key, value, is_causal=causal, scale=scaling,
-                   window_size=int(sliding_window) if (sliding_window and causal) else 0)
-    return out.transpose(1, 2), None
+    window = int(sliding_window) if (sliding_window and causal) else 0
+    out = sdpa_bob(query, key, value, is_causal=causal, scale=scaling, window_size=window)
+    return out.transpose(1, 2).contiguous(), None

@@ -18,7 +18,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libbob_sm100.so"
 SOURCES = ("api.cu", "selftest.cu", "noalloc.cu")
-HEADERS = ("ptx.cuh", "sweep.cuh", "tmap.h")
+HEADERS = ("ptx.cuh", "sweep.cuh", "tmap.h", "internal.h")
 
 
 def _nvcc() -> str:

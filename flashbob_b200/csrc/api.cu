@@ -1,11 +1,13 @@
 // Host side of the C ABI: argument checks, tensor-map construction and kernel dispatch.
-#include "../../include/bob_sm100.h"
+#include "internal.h"
 #include "sweep.cuh"
 #include "tmap.h"
 
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 namespace bob {
 
@@ -15,7 +17,10 @@ enum : int {
     kErrNoDriver = -100,
 };
 
+// The first 256 bytes of every workspace: word 0 = status, words 8.. = work counters of the launches
+// of one call.  The whole block is cleared by each call.
 static constexpr size_t kStatusBlock = 256;
+static constexpr int kCounterWord0 = 8;
 
 static size_t round256(size_t x) { return (x + 255) / 256 * 256; }
 
@@ -29,6 +34,18 @@ static int check_geom(const bob_sm100_geom* g) {
     if (g->window < 0 || (g->window > 0 && !g->is_causal)) return kErrGeom;
     if (g->q_offset < 0 || g->k_offset < 0) return kErrGeom;
     if (!(g->scale > 0.f) || !std::isfinite(g->scale)) return kErrGeom;
+    return 0;
+}
+
+// Results are written with 16-byte stores, pk is read and written as float4.
+static int check_aligned16(std::initializer_list<const void*> ptrs) {
+    for (const void* p : ptrs)
+        if (reinterpret_cast<uintptr_t>(p) % 16) return kErrAlign;
+    return 0;
+}
+static int check_aligned4(std::initializer_list<const void*> ptrs) {
+    for (const void* p : ptrs)
+        if (reinterpret_cast<uintptr_t>(p) % 4) return kErrAlign;
     return 0;
 }
 
@@ -71,7 +88,7 @@ struct TensorArg {
 
 template <int MODE, int DPAD, int TN, bool BF16, int NG = 1, int CW = 16>
 static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, int counter_slot) {
     using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
     using MT = ModeTraits<MODE>;
     auto build = [&](int t, int box_rows) -> int {
@@ -91,7 +108,15 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
         int rc = build(other_tensor<MODE>(i), TN);
         if (rc) return rc;
     }
-    auto kernel = sweep_kernel<MODE, DPAD, TN, BF16, NG, CW>;
+    // The second backward has a build of its own for the usual case of three defined tangents.
+    constexpr bool kSecond = (MODE == kBwd2Row || MODE == kBwd2Col);
+#ifdef BOB_NO_ALLT
+    const bool allt = false;
+#else
+    const bool allt = kSecond && prm.has_uq && prm.has_uk && prm.has_uv;
+#endif
+    auto kernel = allt ? sweep_kernel<MODE, DPAD, TN, BF16, NG, CW, kSecond>
+                       : sweep_kernel<MODE, DPAD, TN, BF16, NG, CW, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CFG::SMEM_BYTES) !=
         cudaSuccess)
         return kErrAttr;
@@ -99,10 +124,8 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
         // The kernel's warpgroups trade registers after launch; the trade only balances (and the
         // pointwise warps' request can only ever be met) if the kernel was built with the register
         // count the trade assumes.  Refuse to launch otherwise.
-        static const int regs_at_launch = [&]() {
-            cudaFuncAttributes a;
-            return cudaFuncGetAttributes(&a, kernel) == cudaSuccess ? a.numRegs : 0;
-        }();
+        cudaFuncAttributes a;
+        const int regs_at_launch = cudaFuncGetAttributes(&a, kernel) == cudaSuccess ? a.numRegs : 0;
         if (regs_at_launch * CFG::NTHREADS < 256 * CFG::REGS_POINTWISE + 128 * CFG::REGS_ROLE) return kErrRegs;
     }
     // CTAs take work items in rounds (see the kernel): gridDim.x items per round.
@@ -114,8 +137,10 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
     // Measured: one persistent CTA per SM is as fast or slightly faster at head dim <= 64; at head dim
     // 128 one CTA per item (the hardware's own dynamic placement) is ~4 % faster than the static
     // alternating assignment, so there the grid covers every item and each CTA runs a single round.
-    const bool persistent = (DPAD == 64);
-    dim3 grid((unsigned)((persistent && items > sms) ? sms : items), 1, 1);
+    const bool persistent = (DPAD == 64) && items > sms;
+    dim3 grid((unsigned)(persistent ? sms : items), 1, 1);
+    // Persistent CTAs take items, longest first, from a counter in the status block (zeroed with it).
+    prm.work_counter = persistent ? prm.status + kCounterWord0 + counter_slot : nullptr;
     kernel<<<grid, CFG::NTHREADS, CFG::SMEM_BYTES, stream>>>(prm);
     return cudaGetLastError() == cudaSuccess ? 0 : kErrLaunch;
 }
@@ -131,37 +156,31 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
 // Second backward: tensor memory (512 columns) leaves room for 32-wide tiles only.
 template <int MODE, bool BF16>
 static int dispatch(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, int counter_slot) {
     constexpr bool kSecond = (MODE == kBwd2Row || MODE == kBwd2Col);
     if (g->D <= 64) {
-        if constexpr (kSecond)           return launch_sweep<MODE, 64, 64, BF16, 1, 32>(g, prm, tensors, stream);
-        else if constexpr (MODE == kFwd) return launch_sweep<MODE, 64, 128, BF16, 2, 128>(g, prm, tensors, stream);
-        else                             return launch_sweep<MODE, 64, 128, BF16, 1, 32>(g, prm, tensors, stream);
+#ifdef BOB_EXP_CW16
+        if constexpr (kSecond)           return launch_sweep<MODE, 64, 64, BF16, 1, 16>(g, prm, tensors, stream, counter_slot);
+#else
+        if constexpr (kSecond)           return launch_sweep<MODE, 64, 64, BF16, 1, 32>(g, prm, tensors, stream, counter_slot);
+#endif
+        else if constexpr (MODE == kFwd) return launch_sweep<MODE, 64, 128, BF16, 2, 128>(g, prm, tensors, stream, counter_slot);
+        else                             return launch_sweep<MODE, 64, 128, BF16, 1, 32>(g, prm, tensors, stream, counter_slot);
     }
-    if constexpr (kSecond)           return launch_sweep<MODE, 128, 32, BF16>(g, prm, tensors, stream);
-    else if constexpr (MODE == kFwd) return launch_sweep<MODE, 128, 64, BF16, 2, 64>(g, prm, tensors, stream);
-    else                             return launch_sweep<MODE, 128, 64, BF16>(g, prm, tensors, stream);
+    if constexpr (kSecond)           return launch_sweep<MODE, 128, 32, BF16>(g, prm, tensors, stream, counter_slot);
+    else if constexpr (MODE == kFwd) return launch_sweep<MODE, 128, 64, BF16, 2, 64>(g, prm, tensors, stream, counter_slot);
+    else                             return launch_sweep<MODE, 128, 64, BF16>(g, prm, tensors, stream, counter_slot);
 }
 
 template <int MODE>
 static int dispatch_dtype(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* tensors,
-                          cudaStream_t stream) {
-    return g->dtype == BOB_SM100_BF16 ? dispatch<MODE, true>(g, prm, tensors, stream)
-                                      : dispatch<MODE, false>(g, prm, tensors, stream);
+                          cudaStream_t stream, int counter_slot) {
+    return g->dtype == BOB_SM100_BF16 ? dispatch<MODE, true>(g, prm, tensors, stream, counter_slot)
+                                      : dispatch<MODE, false>(g, prm, tensors, stream, counter_slot);
 }
 
-// Profiling aid: BOB_SM100_BWD2_KERNELS=row or =col launches only that kernel of the second
-// backward (the column-owned kernel then reads whatever alpha / ecirc the workspace holds).
-static int bwd2_kernel_mask() {
-    const char* e = std::getenv("BOB_SM100_BWD2_KERNELS");
-    if (!e) return 3;
-    if (!std::strcmp(e, "row")) return 1;
-    if (!std::strcmp(e, "col")) return 2;
-    return 3;
-}
-
-// Builds with BOB_PHASE_TIMERS read a device pointer (hex) from BOB_SM100_PHASE_PTR: 24 counters
-// (12 of a pointwise thread, then 12 of the MMA warp).
+// Only builds with -DBOB_PHASE_TIMERS (never the shipped library) read a device pointer (hex) from
+// BOB_SM100_PHASE_PTR: 24 cycle counters (12 of a pointwise thread, then 12 of the MMA warp).
 static long long* phase_pointer() {
 #ifdef BOB_PHASE_TIMERS
     const char* e = std::getenv("BOB_SM100_PHASE_PTR");
@@ -169,6 +188,34 @@ static long long* phase_pointer() {
 #else
     return nullptr;
 #endif
+}
+
+// A per-device word in host memory that kernels can write: a CTA whose bounded wait ran out stores its
+// status code there as well as in the workspace, so the host can notice without synchronising
+// (bob_sm100_last_status).  Page-locked once per device on first use; null if that failed.
+int* sticky_word(int device, bool create) {
+    static std::mutex mu;
+    static int* host[64] = {};
+    static int* dev[64] = {};
+    static bool tried[64] = {};
+    if (device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!tried[device] && create) {
+        tried[device] = true;
+        void* h = nullptr;
+        void* d = nullptr;
+        if (cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+            std::memset(h, 0, 64);
+            if (cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess) {
+                host[device] = static_cast<int*>(h);
+                dev[device] = static_cast<int*>(d);
+            } else {
+                cudaFreeHost(h);
+            }
+        }
+        cudaGetLastError();
+    }
+    return create ? dev[device] : host[device];
 }
 
 static void fill_common(const bob_sm100_geom* g, SweepParams& p, void* workspace) {
@@ -246,26 +293,41 @@ extern "C" int bob_sm100_read_status(const void* workspace, void* stream) {
     return v;
 }
 
+extern "C" int bob_sm100_last_status(int device) {
+    int* w = sticky_word(device, false);
+    if (!w) return 0;
+    return __atomic_exchange_n(w, 0, __ATOMIC_ACQ_REL);
+}
+
+// Clears the status block (status word and work counters) of a call's workspace.
+static int begin_call(void* workspace, cudaStream_t s) {
+    if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256) return kErrWorkspace;
+    return cudaMemsetAsync(workspace, 0, kStatusBlock, s) == cudaSuccess ? 0 : kErrLaunch;
+}
+
 extern "C" int bob_sm100_fwd(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
                              void* out, float* lse, void* workspace, void* stream) {
     int rc = check_geom(g);
     if (rc) return rc;
     if (!q || !k || !v || !out || !lse) return kErrNull;
+    if ((rc = check_aligned16({out}))) return rc;
+    if ((rc = check_aligned4({lse}))) return rc;
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256) return kErrWorkspace;
     DeviceGuard guard(g->device);
     if (!guard.ok) return kErrDevice;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(workspace, 0, sizeof(int), s) != cudaSuccess) return kErrLaunch;
+    if ((rc = begin_call(workspace, s))) return rc;
 
     SweepParams p;
     fill_common(g, p, workspace);
+    p.sticky = sticky_word(g->device, true);
     p.lse = lse;
     p.res0 = out;
     TensorArg t[kNumTensors] = {};
     t[kTQ] = {q, g->q_strides, true};
     t[kTK] = {k, g->k_strides, false};
     t[kTV] = {v, g->v_strides, false};
-    return dispatch_dtype<kFwd>(g, p, t, s);
+    return dispatch_dtype<kFwd>(g, p, t, s, 0);
 }
 
 extern "C" int bob_sm100_bwd1(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
@@ -274,13 +336,15 @@ extern "C" int bob_sm100_bwd1(const bob_sm100_geom* g, const void* q, const void
     int rc = check_geom(g);
     if (rc) return rc;
     if (!q || !k || !v || !out || !lse || !dO || !dQ || !dK || !dV || !delta) return kErrNull;
+    if ((rc = check_aligned16({dQ, dK, dV, pk}))) return rc;
+    if ((rc = check_aligned4({lse, delta}))) return rc;
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256) return kErrWorkspace;
     if ((rc = check_strides(g->out_strides, out))) return rc;
     if ((rc = check_strides(g->do_strides, dO))) return rc;
     DeviceGuard guard(g->device);
     if (!guard.ok) return kErrDevice;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(workspace, 0, sizeof(int), s) != cudaSuccess) return kErrLaunch;
+    if ((rc = begin_call(workspace, s))) return rc;
 
     TensorArg t[kNumTensors] = {};
     t[kTQ] = {q, g->q_strides, true};
@@ -290,35 +354,39 @@ extern "C" int bob_sm100_bwd1(const bob_sm100_geom* g, const void* q, const void
 
     SweepParams p;
     fill_common(g, p, workspace);
+    p.sticky = sticky_word(g->device, true);
     p.lse = const_cast<float*>(lse);
     p.delta = delta;
     p.pk = pk;
     set_strided(p.out, p.out_sb, p.out_sh, p.out_sn, out, g->out_strides);
     set_strided(p.dO, p.dO_sb, p.dO_sh, p.dO_sn, dO, g->do_strides);
     p.res0 = dQ;
-    rc = dispatch_dtype<kBwd1Row>(g, p, t, s);      // dQ and delta
+    rc = dispatch_dtype<kBwd1Row>(g, p, t, s, 0);   // dQ and delta
     if (rc) return rc;
     p.res0 = dK;
     p.res1 = dV;
-    return dispatch_dtype<kBwd1Col>(g, p, t, s);    // dK and dV (reads delta)
+    return dispatch_dtype<kBwd1Col>(g, p, t, s, 1); // dK and dV (reads delta)
 }
 
-extern "C" int bob_sm100_bwd2(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
-                              const void* out, const float* lse, const float* delta, const float* pk,
-                              const void* dO, const void* dQ, const void* uQ, const void* uK, const void* uV,
-                              void* Qbar, void* Kbar, void* Vbar, void* dObar, void* workspace,
-                              void* stream) {
+int bob::bwd2_impl(const bob_sm100_geom* g, const void* q, const void* k, const void* v, const void* out,
+                   const float* lse, const float* delta, const float* pk, const void* dO, const void* dQ,
+                   const void* uQ, const void* uK, const void* uV, void* Qbar, void* Kbar, void* Vbar,
+                   void* dObar, void* workspace, void* stream, int* sticky, int part, bool allow_split) {
+    (void)allow_split;
     int rc = check_geom(g);
     if (rc) return rc;
     if (!q || !k || !v || !out || !lse || !delta || !pk || !dO || !dQ || !Qbar || !Kbar || !Vbar || !dObar)
         return kErrNull;
+    if (part < kPartRow || part > kPartBoth) return kErrGeom;
+    if ((rc = check_aligned16({Qbar, Kbar, Vbar, dObar, pk}))) return rc;
+    if ((rc = check_aligned4({lse, delta}))) return rc;
     if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256) return kErrWorkspace;
     if ((rc = check_strides(g->out_strides, out))) return rc;
     if ((rc = check_strides(g->dq_strides, dQ))) return rc;
     DeviceGuard guard(g->device);
     if (!guard.ok) return kErrDevice;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(workspace, 0, sizeof(int), s) != cudaSuccess) return kErrLaunch;
+    if ((rc = begin_call(workspace, s))) return rc;
 
     TensorArg t[kNumTensors] = {};
     t[kTQ] = {q, g->q_strides, true};
@@ -331,6 +399,7 @@ extern "C" int bob_sm100_bwd2(const bob_sm100_geom* g, const void* q, const void
 
     SweepParams p;
     fill_common(g, p, workspace);
+    p.sticky = sticky;
     p.has_uq = uQ != nullptr; p.has_uk = uK != nullptr; p.has_uv = uV != nullptr;
     p.lse = const_cast<float*>(lse);
     p.delta = const_cast<float*>(delta);
@@ -340,17 +409,38 @@ extern "C" int bob_sm100_bwd2(const bob_sm100_geom* g, const void* q, const void
     p.ecirc = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBlock + stat_bytes);
     set_strided(p.out, p.out_sb, p.out_sh, p.out_sn, out, g->out_strides);
     set_strided(p.dQ, p.dQ_sb, p.dQ_sh, p.dQ_sn, dQ, g->dq_strides);
-    const int mask = bwd2_kernel_mask();
-    if (mask & 1) {
+    if (part & kPartRow) {
         p.res0 = Qbar;
         p.res1 = dObar;
-        rc = dispatch_dtype<kBwd2Row>(g, p, t, s);  // Qbar, dObar, alpha, ecirc
+        rc = dispatch_dtype<kBwd2Row>(g, p, t, s, 0);   // Qbar, dObar, alpha, ecirc
         if (rc) return rc;
     }
-    if (mask & 2) {
+    if (part & kPartCol) {
         p.res0 = Kbar;
         p.res1 = Vbar;
-        rc = dispatch_dtype<kBwd2Col>(g, p, t, s);  // Kbar, Vbar (reads alpha, ecirc)
+        rc = dispatch_dtype<kBwd2Col>(g, p, t, s, 1);   // Kbar, Vbar (reads alpha, ecirc)
     }
     return rc;
+}
+
+size_t bob::bwd2_workspace_bytes_unsplit(const bob_sm100_geom* g) {
+    return kStatusBlock + 2 * round256(static_cast<size_t>(g->B) * g->Hq * g->Nq * sizeof(float));
+}
+
+extern "C" int bob_sm100_bwd2(const bob_sm100_geom* g, const void* q, const void* k, const void* v,
+                              const void* out, const float* lse, const float* delta, const float* pk,
+                              const void* dO, const void* dQ, const void* uQ, const void* uK, const void* uV,
+                              void* Qbar, void* Kbar, void* Vbar, void* dObar, void* workspace,
+                              void* stream) {
+    return bwd2_impl(g, q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, Qbar, Kbar, Vbar, dObar, workspace,
+                     stream, g ? sticky_word(g->device, true) : nullptr, kPartBoth, true);
+}
+
+extern "C" int bob_sm100_bwd2_part(int part, const bob_sm100_geom* g, const void* q, const void* k,
+                                   const void* v, const void* out, const float* lse, const float* delta,
+                                   const float* pk, const void* dO, const void* dQ, const void* uQ,
+                                   const void* uK, const void* uV, void* Qbar, void* Kbar, void* Vbar,
+                                   void* dObar, void* workspace, void* stream) {
+    return bwd2_impl(g, q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, Qbar, Kbar, Vbar, dObar, workspace,
+                     stream, g ? sticky_word(g->device, true) : nullptr, part, true);
 }

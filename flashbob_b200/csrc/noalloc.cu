@@ -12,7 +12,10 @@
 // cleared by each call; the statistics are fully rewritten by the row-owned kernel before the
 // column-owned kernel reads them, so nothing else needs clearing.  Two calls whose kernels overlap
 // on the GPU (different streams, or different host threads) race on the array: serialise them.
-#include "../../include/bob_sm100.h"
+//
+// The status word of the last call on a device is read back with bob_sm100_noalloc_read_status
+// (the array's address is private to this file, so bob_sm100_read_status cannot be used).
+#include "internal.h"
 
 #include <cuda_runtime.h>
 #include <mutex>
@@ -62,10 +65,36 @@ extern "C" int bob_sm100_bwd2_noalloc(const bob_sm100_geom* g, const void* q, co
     if (g->B <= 0 || g->Hq <= 0 || g->Nq <= 0) return -2;
     const size_t rows = static_cast<size_t>(g->B) * static_cast<size_t>(g->Hq) * static_cast<size_t>(g->Nq);
     if (rows > kMaxRows) return -12;                               // larger than the built-in scratch
-    if (bob_sm100_workspace_bytes(BOB_SM100_STAGE_BWD2, g) > kNoAllocScratchBytes) return -12;
+    if (bob::bwd2_workspace_bytes_unsplit(g) > kNoAllocScratchBytes) return -12;
     void* scratch = nullptr;
     const int rc = scratch_address(g->device, &scratch);
     if (rc) return rc;
-    return bob_sm100_bwd2(g, q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, Qbar, Kbar, Vbar, dObar,
-                          scratch, stream);
+    // no host-visible status word (its set-up page-locks memory) and no division of long work items
+    // (that needs a larger workspace): this path touches nothing but the fixed array
+    return bob::bwd2_impl(g, q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, Qbar, Kbar, Vbar, dObar,
+                          scratch, stream, nullptr, bob::kPartBoth, false);
+}
+
+// Waits for `stream`, then returns the status word the last bob_sm100_bwd2_noalloc call on `device`
+// left in the built-in scratch (0 = every wait completed; also 0 if no call has run there yet).
+// Allocates nothing.
+extern "C" int bob_sm100_noalloc_read_status(int device, void* stream) {
+    if (device < 0 || device >= kMaxDevices) return -7;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        scratch = g_scratch_addr[device];
+    }
+    if (!scratch) return 0;
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) return -7;
+    if (prev != device && cudaSetDevice(device) != cudaSuccess) return -7;
+    int v = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = 0;
+    if (cudaMemcpyAsync(&v, scratch, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess)
+        rc = -8;
+    if (prev != device) cudaSetDevice(prev);
+    return rc ? rc : v;
 }

@@ -9,6 +9,7 @@
 //   out[7] = A''* B^T  A'' written to tensor memory by threads and read from there (derived
 //                      operands that never touch shared memory)
 // A is [128, 64], B is [64, 64], both fp16 or both bf16 (kind::f16 needs one format for A and B).
+#include "internal.h"
 #include "ptx.cuh"
 #include "tmap.h"
 
@@ -166,7 +167,7 @@ selftest_kernel(const __grid_constant__ SelftestMaps maps, const uint16_t* __res
 }
 
 // A wait that nothing completes: the bounded wait must give up and report, not spin forever.
-__global__ void timeout_selftest_kernel(int* __restrict__ status) {
+__global__ void timeout_selftest_kernel(int* __restrict__ status, int* sticky) {
     __shared__ __align__(8) unsigned long long bar;
     const uint32_t b = smem_u32(&bar);
     if (threadIdx.x == 0) {
@@ -175,7 +176,11 @@ __global__ void timeout_selftest_kernel(int* __restrict__ status) {
     }
     __syncthreads();
     const bool done = mbar_wait(b, 0);          // nobody arrives on this barrier
-    if (threadIdx.x == 0) atomicExch(status, done ? 0 : kSelftestTimedOut);
+    if (threadIdx.x == 0) {
+        atomicExch(status, done ? 0 : kSelftestTimedOut);
+        // the same second report the attention kernels make when they give up
+        if (!done && sticky) { *reinterpret_cast<volatile int*>(sticky) = kSelftestTimedOut; __threadfence_system(); }
+    }
 }
 
 }  // namespace bob
@@ -184,7 +189,9 @@ extern "C" int bob_sm100_timeout_selftest(int* status, void* stream) {
     if (!status) return -1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess) return -3;
-    bob::timeout_selftest_kernel<<<1, 32, 0, s>>>(status);
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return -7;
+    bob::timeout_selftest_kernel<<<1, 32, 0, s>>>(status, bob::sticky_word(device, true));
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

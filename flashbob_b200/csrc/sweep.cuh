@@ -15,9 +15,11 @@
 // holds column j of the score matrix and the operands come out already transposed; the per-query
 // statistics then vary along the tensor-memory columns and are staged in shared memory.
 //
-// Warp roles: 128*NSPLIT pointwise threads, one MMA-issuing thread, one TMA-producing thread.
-// Tiles of the other side are double buffered; scores of tile t+1 are issued before the output
-// products of tile t, so the tensor pipe works while the pointwise threads convert tile t.
+// Warp roles: NG groups of 128*NSPLIT pointwise threads, one MMA warp (warp-uniform control flow, one
+// elected lane issues) and one TMA warp.  Tiles of the other side sit in a ring of 2 to 6 stages;
+// the scores of tile t+1 are issued before the output products of tile t, so the tensor pipe works
+// while the pointwise threads convert tile t.  Work items (own tile x head x batch) are handed out
+// longest first, either from a global counter (persistent launches) or one per CTA.
 //
 // The algebra follows the reference's second backward (reference: src/bob/kernels/common.py:15-30
 // for the formulas, :463-654 for the row-owned tile body and epilogue, :661-786 for the
@@ -71,6 +73,8 @@ struct SweepParams {
     void* res1;
     void* res2;
     int* status;
+    int* sticky;                  // optional second word that a CTA giving up also writes (host-visible memory)
+    int* work_counter;            // persistent launches: next work item (zeroed by the host); null: one item per CTA
     long long* phase_cycles;      // optional cycle counters per pipeline phase (builds with BOB_PHASE_TIMERS)
 };
 
@@ -160,9 +164,10 @@ struct SweepConfig {
     static constexpr int OFF_STAT = OFF_OTH + NSTAGE * OTH_STAGE_BYTES;         // [NSTAGE][4][TN] floats
     static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [2][NG * NSPLIT][128] floats
     static constexpr int OFF_BAR = OFF_RED + (MODE == kFwd ? 4 : 2) * NG * NSPLIT * 128 * 4;   // forward: two copies
-    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG;
-    static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag
-    static constexpr int OFF_IO = (OFF_MISC + 16 + 127) & ~127;                 // staged epilogue operands
+    static constexpr int RING = 4;                                              // work items announced ahead
+    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG + 2 * RING;
+    static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag, item ring
+    static constexpr int OFF_IO = (OFF_MISC + 16 + 4 * RING + 127) & ~127;      // staged epilogue operands
     static constexpr int SMEM_BYTES = OFF_IO + IO_BYTES + 1024;                 // + alignment slack
     static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
 };
@@ -221,13 +226,16 @@ __device__ __forceinline__ void store16_from_float(void* base, long long elem_of
 template <bool V> struct BoolTag { static constexpr bool value = V; };
 template <int V> struct IntTag { static constexpr int value = V; };
 
-template <int MODE, int DPAD, int TN, bool BF16, int NG, int CW>
+template <int MODE, int DPAD, int TN, bool BF16, int NG, int CW, bool ALLT = false>
 __global__ void __launch_bounds__(SweepConfig<MODE, DPAD, TN, NG, CW>::NTHREADS, 1)
 sweep_kernel(const __grid_constant__ SweepParams p) {
+    static_assert(!ALLT || MODE == kBwd2Row || MODE == kBwd2Col, "only the second backward has tangents");
     using CFG = SweepConfig<MODE, DPAD, TN, NG, CW>;
     static_assert(CW == 16 || CW == 32 || (CW == 64 && MODE <= kBwd1Col) || (CW == 128 && MODE == kFwd),
                   "16 or 32 columns per pointwise thread (first backward: also 64; forward: 64 or 128)");
-    constexpr int RW = 16;                     // columns per round of tensor-memory loads
+    // columns per round of tensor-memory loads (8 where 512 pointwise threads share the second
+    // backward's tile: four loaded accumulators and four packed operands must fit 112 registers)
+    constexpr int RW = ((MODE == kBwd2Row || MODE == kBwd2Col) && CW == 16 && TN == 64) ? 8 : 16;
     using MT = ModeTraits<MODE>;
     constexpr int NSPLIT = CFG::NSPLIT, NPW = CFG::NPW, GP = CFG::GP, NSTAGE = CFG::NSTAGE, KSUB = CFG::KSUB;
     constexpr bool COL = MT::COL;
@@ -256,6 +264,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     auto bar_op_full = [&](int g) { return bar_grp0 + 40u * g + 16; };        //   operands written
     auto bar_op_empty = [&](int g) { return bar_grp0 + 40u * g + 24; };       //   operands consumed
     auto bar_pw = [&](int g) { return bar_grp0 + 40u * g + 32; };             //   the group's own threads
+    const uint32_t bar_ring0 = bar_grp0 + 40u * NG;
+    auto bar_item_full = [&](int s) { return bar_ring0 + 8u * s; };           // ring slot announced
+    auto bar_item_empty = [&](int s) { return bar_ring0 + 8u * (CFG::RING + s); };   // ring slot read by every follower
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -278,7 +289,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     // kernel parameters that the per-tile code needs, read once
     const bool causal = p.is_causal != 0;
     const int window = p.window;
-    const bool has_uq = p.has_uq != 0, has_uk = p.has_uk != 0, has_uv = p.has_uv != 0;
+    // ALLT (second backward): all three tangents are defined, the usual case.  Their flags are then
+    // compile-time constants, so the loads and arithmetic of F and C are unconditional instead of
+    // predicated on values only known at run time.
+    const bool has_uq = ALLT || p.has_uq != 0, has_uk = ALLT || p.has_uk != 0, has_uv = ALLT || p.has_uv != 0;
     struct Item { int own0, head, batch, kv_head, t_lo, t_hi, T, total; };
     auto decode = [&](int item) {
         Item w;
@@ -307,13 +321,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         w.total = w.T * n_outer;
         return w;
     };
-    // Round r of this CTA: rounds alternate direction over the longest-first item list, so that a CTA
-    // that got a long item in one round gets a short one in the next.  -1: no item in this round.
-    const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
-    auto item_of = [&](int r) {
-        const int i = r * (int)gridDim.x + ((r & 1) ? ((int)gridDim.x - 1 - (int)blockIdx.x) : (int)blockIdx.x);
-        return i < n_items ? i : -1;
-    };
+    // Which items this CTA works on.  The TMA warp decides: with a work counter (persistent launch)
+    // it takes the next item of the longest-first list from the counter, otherwise the CTA has the
+    // single item blockIdx.x.  It announces each item (then -1 = no more) in a ring of RING slots in
+    // shared memory; the MMA warp and the pointwise warps follow the ring.
+    constexpr int RING = CFG::RING;
+    volatile int* item_ring = reinterpret_cast<volatile int*>(sptr + CFG::OFF_MISC + 16);
 #define BOB_ITEM_LOCALS(w)                                                                         \
     const int own0 = (w).own0, head = (w).head, batch = (w).batch, kv_head = (w).kv_head;         \
     const int t_lo = (w).t_lo, t_hi = (w).t_hi, T = (w).T, total = (w).total;                      \
@@ -333,6 +346,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         mbar_init(bar_done, 1);
         mbar_init(bar_pw_all, NPW / 32);
         mbar_init(bar_out_free, NPW / 32);
+        for (int s = 0; s < CFG::RING; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), 1 + NPW / 32); }
         misc[1] = 0;
         mbar_fence_init();
     }
@@ -343,7 +357,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem = misc[0];
+    const uint32_t tmem = __shfl_sync(0xffffffffu, misc[0], 0);      // warp-uniform, and known to be
     // [scores of group 0 .. NG-1 | operands of group 0 .. NG-1 | output accumulators]
     const uint32_t tmem_oper = tmem + NG * CFG::SC_COLS;
     const uint32_t tmem_out = tmem_oper + NG * CFG::OPER_COLS;
@@ -351,6 +365,17 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     auto give_up = [&](int code) {
         misc[1] = 1;
         atomicCAS(p.status, 0, code);
+        if (p.sticky) { *reinterpret_cast<volatile int*>(p.sticky) = code; __threadfence_system(); }
+    };
+    // Followers of the item ring: the k-th announced item (-1: none left; -2: the wait ran out).
+    auto follow_ring = [&](int k) -> int {
+        const int slot = k % RING;
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_item_full(slot), (k / RING) & 1))) return -2;
+        // every lane reads the same word; the broadcast tells the compiler that the value (and all
+        // the loop bounds and addresses derived from it) is uniform across the warp
+        const int item = __shfl_sync(0xffffffffu, item_ring[slot], 0);
+        if (lane == 0) mbar_arrive(bar_item_empty(slot));
+        return item;
     };
     auto aborted = [&]() { return misc[1] != 0; };
 
@@ -373,9 +398,27 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         int s = 0, round = 0;                    // pipeline stage of tile `cnt`, and cnt / NSTAGE
         int n_live = 0;                          // items with at least one tile started so far
         bool alive = true;
-        for (int r = 0; alive && r < n_rounds; ++r) {
-            const int item = item_of(r);
-            if (item < 0) continue;
+        for (int k_item = 0; alive; ++k_item) {
+            const int slot = k_item % RING;
+            if (k_item >= RING &&
+                !__all_sync(0xffffffffu, mbar_wait(bar_item_empty(slot), (k_item / RING - 1) & 1))) {
+                if (lane == 0) give_up(kStatusTimeoutLoad);
+                break;
+            }
+            int item = -1;
+            if (lane == 0) {
+#ifdef BOB_STATIC_ITEMS
+                if (p.work_counter) item = k_item * (int)gridDim.x + ((k_item & 1) ? ((int)gridDim.x - 1 - (int)blockIdx.x) : (int)blockIdx.x);
+#else
+                if (p.work_counter) item = atomicAdd(p.work_counter, 1);
+#endif
+                else if (k_item == 0) item = (int)blockIdx.x;
+                if (item < 0 || item >= n_items) item = -1;
+                item_ring[slot] = item;
+                mbar_arrive(bar_item_full(slot));
+            }
+            item = __shfl_sync(0xffffffffu, item, 0);
+            if (item < 0) break;
             const Item w = decode(item);
             BOB_ITEM_LOCALS(w)
             if (total == 0) continue;
@@ -471,11 +514,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 constexpr uint32_t idesc = umma_idesc(fmt, fmt, NS * TN, false);
                 const uint32_t a = own16 + ((slot_a * CFG::OWN_TILE_BYTES) >> 4);
                 const uint32_t b = stage16 + ((slot_b * CFG::OTH_SUB_BYTES) >> 4);
-                #pragma unroll
-                for (int ks = 0; ks < DPAD / 16; ++ks) {
-                    const uint32_t ao = ((ks / 4) * (128 * 128) + (ks % 4) * 32) >> 4;
-                    const uint32_t bo = ((ks / 4) * (MT::NOTH * CFG::OTH_SUB_BYTES) + (ks % 4) * 32) >> 4;
-                    if (elect_one()) umma_ss_lo(sc_base + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
+                if (elect_one()) {
+                    #pragma unroll
+                    for (int ks = 0; ks < DPAD / 16; ++ks) {
+                        const uint32_t ao = ((ks / 4) * (128 * 128) + (ks % 4) * 32) >> 4;
+                        const uint32_t bo = ((ks / 4) * (MT::NOTH * CFG::OTH_SUB_BYTES) + (ks % 4) * 32) >> 4;
+                        umma_ss_lo(sc_base + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
+                    }
                 }
             };
             // output-shaped product: out[128, DPAD] (+)= operand[oper] * other[slot_b]; the operand is
@@ -488,9 +533,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 constexpr uint32_t lbo16 = (KSUB > 1) ? ((MT::NOTH * CFG::OTH_SUB_BYTES) >> 4) : 1u;
                 const uint32_t a = op_base + oper * CFG::OPER_COLS_EACH;
                 const uint32_t b = (stage16 - 0x10000u) + (lbo16 << 16) + ((slot_b * CFG::OTH_SUB_BYTES) >> 4);
-                #pragma unroll
-                for (int ks = 0; ks < TN / 16; ++ks) {
-                    if (elect_one())
+                if (elect_one()) {
+                    #pragma unroll
+                    for (int ks = 0; ks < TN / 16; ++ks)
                         umma_ts_lo(tmem_out + out * DPAD, a + ks * 8, b + ((ks * 2048) >> 4), idesc,
                                    (accumulate || ks > 0) ? 1u : 0u);
                 }
@@ -542,9 +587,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             int n_out0 = 0, n_out1 = 0;               // output rounds issued so far, per pointwise group
             int n_live = 0;                           // items with at least one tile finished so far
             bool ok = true;
-            for (int r = 0; ok && r < n_rounds; ++r) {
-            const int item = item_of(r);
-            if (item < 0) continue;
+            for (int k_item = 0; ok; ++k_item) {
+            const int item = follow_ring(k_item);
+            if (item == -2) give_up(kStatusTimeoutMma);
+            if (item < 0) break;
             const Item w = decode(item);
             BOB_ITEM_LOCALS(w)
             if (total == 0) continue;
@@ -666,9 +712,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         int n_items_done = 0;                    // items finished so far, with or without tiles
         BOB_PH_DECL
 
-        for (int r = 0; ok && r < n_rounds; ++r) {
-            const int item = item_of(r);
-            if (item < 0) continue;
+        for (int k_item = 0; ok; ++k_item) {
+            const int item = follow_ring(k_item);
+            if (item == -2) give_up(kStatusTimeoutPw);
+            if (item < 0) break;
         const Item w = decode(item);
         BOB_ITEM_LOCALS(w)
         const int own_idx = own0 + row;
@@ -887,8 +934,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 constexpr int NB = LOAD_ALL ? R : 1;
                 const float2 cexp2 = make_float2(c_exp, c_exp);
                 const float2 scale2 = make_float2(p.scale, p.scale);
-                const bool has_f = BWD2 && (has_uq || has_uk);
-                const bool has_c = BWD2 && has_uv;
+                const bool has_f = BWD2 && (ALLT || has_uq || has_uk);
+                const bool has_c = BWD2 && (ALLT || has_uv);
                 float in_s[NB][RW], in_dp[NB][RW], in_f[NB][RW], in_c[NB][RW];
                 auto issue_loads = [&](int r, int b) {
                     const int cb = col0 + RW * r;
@@ -913,6 +960,23 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 } else {
                     issue_loads(0, 0);
                 }
+#ifdef BOB_STORE_LATE
+                constexpr bool STORE_LATE = LOAD_ALL;    // all rounds' arithmetic first, then the wait and the stores
+#else
+                constexpr bool STORE_LATE = false;
+#endif
+                uint32_t wbuf[STORE_LATE ? R : 1][4][RW / 2];
+                auto store_round = [&](int half) {
+                    const uint32_t dst = op_taddr + (RW / 2) * half;     // RW / 2 packed words per round
+                    auto st = [&](uint32_t addr, const uint32_t* w) {
+                        if constexpr (RW == 16) tmem_st8(addr, w); else tmem_st4(addr, w);
+                    };
+                    const int wb = STORE_LATE ? half : 0;
+                    st(dst + 0 * CFG::OPER_COLS_EACH, wbuf[wb][0]);
+                    if constexpr (MT::NOPER > 1) st(dst + 1 * CFG::OPER_COLS_EACH, wbuf[wb][1]);
+                    if constexpr (MT::NOPER > 2) st(dst + 2 * CFG::OPER_COLS_EACH, wbuf[wb][2]);
+                    if constexpr (MT::NOPER > 3) st(dst + 3 * CFG::OPER_COLS_EACH, wbuf[wb][3]);
+                };
                 #pragma unroll
                 for (int half = 0; half < R; ++half) {            // `half` = round of RW columns
                     const int cb = col0 + RW * half;
@@ -936,41 +1000,58 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                             for (int c = 0; c < RW; ++c) cc_[c] = 0.f;
                         }
                     }
-                    uint32_t w0[RW / 2], w1[RW / 2], w2[RW / 2], w3[RW / 2];
-                    (void)w2; (void)w3;
+                    uint32_t* w0 = wbuf[STORE_LATE ? half : 0][0];
+                    uint32_t* w1 = wbuf[STORE_LATE ? half : 0][1];
+                    uint32_t* w2 = wbuf[STORE_LATE ? half : 0][2];
+                    uint32_t* w3 = wbuf[STORE_LATE ? half : 0][3];
+                    (void)w1; (void)w2; (void)w3;
                     // negated statistics of these columns (column-owned modes), four columns per load
                     const float4* sb4 = reinterpret_cast<const float4*>(stat_buf + stage * 4 * TN + cb);
-                    #pragma unroll
-                    for (int c4 = 0; c4 < RW / 4; ++c4) {
-                        float4 q_l2, q_dl, q_al, q_ec;
+                    // The arithmetic of four columns (two packed pairs) in two steps, so that the
+                    // exponentials of the next four columns can be issued before the multiplications of
+                    // these four: probabilities first, then everything that needs them.
+                    struct Grp { float2 pr[2]; float4 q_dl, q_al, q_ec; };
+                    auto exps = [&](int c4) {
+                        Grp gq;
+                        float4 q_l2;
                         if constexpr (COL) {
-                            q_l2 = sb4[c4]; q_dl = sb4[TN / 4 + c4];
-                            if constexpr (MODE == kBwd2Col) { q_al = sb4[2 * (TN / 4) + c4]; q_ec = sb4[3 * (TN / 4) + c4]; }
+                            q_l2 = sb4[c4]; gq.q_dl = sb4[TN / 4 + c4];
+                            if constexpr (MODE == kBwd2Col) { gq.q_al = sb4[2 * (TN / 4) + c4]; gq.q_ec = sb4[3 * (TN / 4) + c4]; }
                         }
                         #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const int c = 4 * c4 + 2 * h;          // columns c, c + 1 of this round
-                            const int wi = c >> 1;                 // packed word index inside this round
+                            const int c = 4 * c4 + 2 * h;
                             const int mc = RW * half + c;          // bit index in vmask
-                            float2 nl2, ndl, nal, nec;
-                            (void)nal; (void)nec;
-                            if constexpr (COL) {
-                                nl2 = h ? make_float2(q_l2.z, q_l2.w) : make_float2(q_l2.x, q_l2.y);
-                                ndl = h ? make_float2(q_dl.z, q_dl.w) : make_float2(q_dl.x, q_dl.y);
-                                if constexpr (MODE == kBwd2Col) {
-                                    nal = h ? make_float2(q_al.z, q_al.w) : make_float2(q_al.x, q_al.y);
-                                    nec = h ? make_float2(q_ec.z, q_ec.w) : make_float2(q_ec.x, q_ec.y);
-                                }
-                            } else {
-                                nl2 = make_float2(nL2, nL2);
-                                ndl = make_float2(ndlt, ndlt);
-                            }
+                            float2 nl2;
+                            if constexpr (COL) nl2 = h ? make_float2(q_l2.z, q_l2.w) : make_float2(q_l2.x, q_l2.y);
+                            else nl2 = make_float2(nL2, nL2);
                             const float2 x = __ffma2_rn(make_float2(s_[c], s_[c + 1]), cexp2, nl2);
                             float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
                             if constexpr (!FULL) {
                                 pr.x = ((vmask >> mc) & 1u) ? pr.x : 0.f;
                                 pr.y = ((vmask >> (mc + 1)) & 1u) ? pr.y : 0.f;
                             }
+                            gq.pr[h] = pr;
+                        }
+                        return gq;
+                    };
+                    auto math = [&](int c4, const Grp& gq) {
+                        #pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int c = 4 * c4 + 2 * h;          // columns c, c + 1 of this round
+                            const int wi = c >> 1;                 // packed word index inside this round
+                            float2 ndl, nal, nec;
+                            (void)nal; (void)nec;
+                            if constexpr (COL) {
+                                ndl = h ? make_float2(gq.q_dl.z, gq.q_dl.w) : make_float2(gq.q_dl.x, gq.q_dl.y);
+                                if constexpr (MODE == kBwd2Col) {
+                                    nal = h ? make_float2(gq.q_al.z, gq.q_al.w) : make_float2(gq.q_al.x, gq.q_al.y);
+                                    nec = h ? make_float2(gq.q_ec.z, gq.q_ec.w) : make_float2(gq.q_ec.x, gq.q_ec.y);
+                                }
+                            } else {
+                                ndl = make_float2(ndlt, ndlt);
+                            }
+                            const float2 pr = gq.pr[h];
                             const float2 dps = __fadd2_rn(make_float2(dp_[c], dp_[c + 1]), ndl);
                             if constexpr (MODE == kBwd1Row) {
                                 const float2 ds = __fmul2_rn(pr, dps);
@@ -1004,25 +1085,47 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                                 w2[wi] = pack2<BF16>(ph.x, ph.y);                         // (P*(F-alpha))^T
                             }
                         }
+                    };
+#ifdef BOB_SWP
+                    {
+                        Grp cur = exps(0);
+                        #pragma unroll
+                        for (int c4 = 0; c4 < RW / 4; ++c4) {
+                            Grp nxt = cur;
+                            if (c4 + 1 < RW / 4) {
+                                nxt = exps(c4 + 1);
+                                // keeps the order: these exponentials are issued before the products below
+                                asm volatile("" : "+f"(nxt.pr[0].x), "+f"(nxt.pr[0].y), "+f"(nxt.pr[1].x), "+f"(nxt.pr[1].y));
+                            }
+                            math(c4, cur);
+                            if (c4 + 2 < RW / 4) {
+                                // ... and the exponentials after the next ones not before these products
+                                const int cn = 4 * (c4 + 2);
+                                asm volatile("" : "+r"(w0[2 * c4 + 1]), "+f"(s_[cn]), "+f"(s_[cn + 1]), "+f"(s_[cn + 2]), "+f"(s_[cn + 3]));
+                            }
+                            cur = nxt;
+                        }
                     }
+#else
+                    #pragma unroll
+                    for (int c4 = 0; c4 < RW / 4; ++c4) math(c4, exps(c4));
+#endif
                     if constexpr (!LOAD_ALL) {
                         if (half + 1 < R) issue_loads(half + 1, 0);
                     }
-                    if (half == 0) {
+                    if (STORE_LATE ? (half + 1 == R) : (half == 0)) {
                         BOB_PH(2)
                         // the previous tile's output products must have consumed its operands
                         if (n_op > 0 && !pw_wait(bar_op_empty(grp), (n_op - 1) & 1)) return false;
                         BOB_PH(3)
                     }
-                    {
-                        const uint32_t dst = op_taddr + (RW / 2) * half;     // RW / 2 packed words per round
-                        auto st = [&](uint32_t addr, const uint32_t* w) {
-                            if constexpr (RW == 16) tmem_st8(addr, w); else tmem_st4(addr, w);
-                        };
-                        st(dst + 0 * CFG::OPER_COLS_EACH, w0);
-                        if constexpr (MT::NOPER > 1) st(dst + 1 * CFG::OPER_COLS_EACH, w1);
-                        if constexpr (MT::NOPER > 2) st(dst + 2 * CFG::OPER_COLS_EACH, w2);
-                        if constexpr (MT::NOPER > 3) st(dst + 3 * CFG::OPER_COLS_EACH, w3);
+                    if constexpr (STORE_LATE) {
+                        if (half + 1 == R) {
+                            #pragma unroll
+                            for (int r = 0; r < R; ++r) store_round(r);
+                        }
+                    } else {
+                        store_round(half);
                     }
                 }
             }

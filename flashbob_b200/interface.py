@@ -112,18 +112,21 @@ def _check_scalars(is_causal, scale, window_size, q_offset, k_offset):
 
 
 def _check_grouped(q, k, *, window: int, rectangular: bool) -> None:
+    """Rejections for grouped heads, in the reference's order: a rectangle is refused first
+    (reference: src/bob/sdpa.py:429-433), then CPU tensors, a dtype other than bf16, a window and a
+    group larger than 32 (reference: src/bob/sdpa.py:129-137).  With ALLOW_WIDENED_GQA only the CPU
+    and group-size limits remain."""
+    if rectangular and not ALLOW_WIDENED_GQA:
+        raise NotImplementedError("FlashBoB GQA/MQA does not support rectangular attention")
     if not q.is_cuda:
         raise NotImplementedError("FlashBoB GQA/MQA requires CUDA")
+    if not ALLOW_WIDENED_GQA:
+        if q.dtype != torch.bfloat16:
+            raise TypeError("FlashBoB GQA/MQA requires bfloat16")
+        if window > 0:
+            raise NotImplementedError("FlashBoB GQA/MQA does not support sliding windows")
     if q.shape[1] // k.shape[1] > _MAX_GROUP:
         raise NotImplementedError(f"FlashBoB GQA/MQA supports grouping factors up to {_MAX_GROUP}")
-    if ALLOW_WIDENED_GQA:
-        return
-    if rectangular:
-        raise NotImplementedError("FlashBoB GQA/MQA does not support rectangular attention")
-    if q.dtype != torch.bfloat16:
-        raise TypeError("FlashBoB GQA/MQA requires bfloat16")
-    if window > 0:
-        raise NotImplementedError("FlashBoB GQA/MQA does not support sliding windows")
 
 
 def _resolve_q_offset(n_q: int, n_k: int, q_offset, k_offset: int, is_causal: bool) -> int:

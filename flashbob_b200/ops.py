@@ -68,9 +68,30 @@ def _workspace(stage: int, g: _lib.Geom, device) -> torch.Tensor:
 
 
 def _finish(ws: torch.Tensor, device, what: str) -> None:
+    """Raise if a kernel on this device gave up on a bounded wait.
+
+    Default: a non-blocking look at the device's host-visible status word, which a kernel writes as
+    it gives up - so a time-out of an earlier call surfaces here, at the latest one call late, without
+    any synchronisation.  With BOB_SM100_CHECK_STATUS=1 the call's own status word is read back
+    after waiting for the stream (exact attribution, one synchronisation per call).
+    """
+    lib = _lib.load()
     if _CHECK_STATUS:
-        st = _lib.load().bob_sm100_read_status(_ptr(ws), _stream(device))
-        _lib.check(st, f"{what} (device status)")
+        _lib.check(lib.bob_sm100_read_status(_ptr(ws), _stream(device)), f"{what} (device status)")
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    st = lib.bob_sm100_last_status(index)
+    if st:
+        _lib.check(st, f"an earlier libbob_sm100 kernel on cuda:{index} (seen after {what}; its results are undefined)")
+
+
+def check_device_status(device=None) -> None:
+    """Raise if any libbob_sm100 kernel on `device` gave up on a bounded wait since the last check.
+    Non-blocking; call it after a synchronisation point (for instance at the end of a training step)
+    to be sure that every kernel launched before it is covered."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    st = _lib.load().bob_sm100_last_status(index)
+    if st:
+        _lib.check(st, f"a libbob_sm100 kernel on cuda:{index}")
 
 
 def _require_cuda_16bit(*tensors) -> None:

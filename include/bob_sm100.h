@@ -27,7 +27,8 @@
  *     w > 0 additionally requires query position - key position < w.
  *   - Hq must be a multiple of Hkv; query head h uses KV head h / (Hq / Hkv); dK, dV, Kbar and
  *     Vbar are summed over the query heads of a group.
- *   - D must be a multiple of 16, at most 128.
+ *   - D must be a multiple of 16, at most 128.  Result pointers and pk must be 16-byte aligned,
+ *     lse and delta 4-byte aligned (checked on the host: error -10).
  *   - No entry point allocates or frees device memory (except bob_sm100_selftest's caller-owned
  *     buffers, which are arguments too).  Scratch is passed in as `workspace`, at least
  *     bob_sm100_workspace_bytes(stage, geom) bytes, 256-byte aligned.  Its first word is a
@@ -88,6 +89,14 @@ int bob_sm100_kernel_launches(int stage, const bob_sm100_geom* geom);
 /* Waits for `stream`, then returns the status word of `workspace` (0 = every wait completed). */
 int bob_sm100_read_status(const void* workspace, void* stream);
 
+/* Non-blocking check (no counterpart in the reference): returns and clears the code of the most
+ * recent bounded wait that ran out in any bob_sm100_fwd / bwd1 / bwd2 kernel on `device` since the
+ * last check, 0 if none.  Kernels write the code into a page-locked host word as they give up, so
+ * the host can poll it between calls without synchronising; a time-out is therefore seen at the
+ * latest when the caller checks after its next synchronisation, and typically one call late.  The
+ * results of a call whose kernel gave up are undefined. */
+int bob_sm100_last_status(int device);
+
 /* Forward: out = softmax(scale * q k^T + mask) v and lse. */
 int bob_sm100_fwd(const bob_sm100_geom* geom, const void* q, const void* k, const void* v,
                   void* out, float* lse, void* workspace, void* stream);
@@ -107,6 +116,17 @@ int bob_sm100_bwd2(const bob_sm100_geom* geom, const void* q, const void* k, con
                    const void* dO, const void* dQ, const void* uQ, const void* uK, const void* uV,
                    void* Qbar, void* Kbar, void* Vbar, void* dObar, void* workspace, void* stream);
 
+/* Profiling aid (no counterpart in the reference): bob_sm100_bwd2 restricted to one of its two
+ * kernels.  part = 1: only the row-owned kernel (Qbar, dObar and the row statistics in the
+ * workspace); part = 2: only the column-owned kernel (Kbar, Vbar; it reads the row statistics a
+ * previous part-1 or full call left in the same workspace); part = 3: both, i.e. bob_sm100_bwd2.
+ * Results that the skipped kernel would have produced are left untouched. */
+int bob_sm100_bwd2_part(int part, const bob_sm100_geom* geom, const void* q, const void* k,
+                        const void* v, const void* out, const float* lse, const float* delta,
+                        const float* pk, const void* dO, const void* dQ, const void* uQ,
+                        const void* uK, const void* uV, void* Qbar, void* Kbar, void* Vbar,
+                        void* dObar, void* workspace, void* stream);
+
 /* Second backward without a caller-provided workspace (no counterpart in the reference).
  * For hosts that cannot allocate or hand over scratch memory at call time - a plug-in inside a
  * runtime that owns all device memory, a loop that forbids allocator calls after start-up.  The
@@ -123,6 +143,10 @@ int bob_sm100_bwd2_noalloc(const bob_sm100_geom* geom, const void* q, const void
                            const void* dO, const void* dQ, const void* uQ, const void* uK,
                            const void* uV, void* Qbar, void* Kbar, void* Vbar, void* dObar,
                            void* stream);
+/* Status word of the last bob_sm100_bwd2_noalloc call on `device` (waits for `stream` first; 0 =
+ * every wait completed).  The built-in scratch has no address a caller could pass to
+ * bob_sm100_read_status, hence this reader.  Allocates nothing. */
+int bob_sm100_noalloc_read_status(int device, void* stream);
 
 /* Known-answer check of the tensor-core plumbing: a [128,64] x b [64,64] (same 16-bit format).
  * out is fp32 [8,128,64]: out[0] = a b^T; out[1] = a b; out[2] = a b^T with a staged through
@@ -134,7 +158,8 @@ int bob_sm100_selftest(const void* a, const void* b, int is_bf16, float* out, in
 
 /* Failure-detection check: launches one warp that waits on a barrier nothing completes.  The
  * library's bounded wait gives up after about half a second of SM cycles and the kernel writes 77
- * to *status (a device int) and returns normally; the context stays usable. */
+ * to *status (a device int) and to the current device's host-visible status word (see
+ * bob_sm100_last_status) and returns normally; the context stays usable. */
 int bob_sm100_timeout_selftest(int* status, void* stream);
 
 #ifdef __cplusplus

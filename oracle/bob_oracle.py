@@ -251,22 +251,101 @@ def bob_closed_form(q, k, v, dO, uQ, uK, uV, *, dtype=torch.float64, is_causal=F
                     ecirc=ecirc, Qbar=Qbar, Kbar=red(Kbarx), Vbar=red(Vbarx), dObar=dObar)
 
 
+def bob_closed_form_streamed(q, k, v, dO, uQ, uK, uV, *, dtype=torch.float64, is_causal=False,
+                             scale=None, window_size=0, q_offset=None, k_offset=0, row_block=1024):
+    """`bob_closed_form` for sequences whose [Nq, Nk] score matrices do not fit in memory at once.
+
+    Same formulas, evaluated one query head at a time and `row_block` query rows at a time (every
+    row statistic is local to its row, so a block of whole rows is self-contained); the key-side
+    results dK, dV, Kbar, Vbar are accumulated over the row blocks and over the query heads of a KV
+    group.  This is how the largest benchmark configuration is checked: one (batch, KV head) unit,
+    one query head at a time (the score matrices of one head alone take 512 MiB each in fp64).
+    """
+    B, Hq, Nq, D = q.shape
+    Hkv, Nk = k.shape[1], k.shape[2]
+    G = Hq // Hkv
+    t = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    q_offset = infer_q_offset(Nq, Nk, q_offset, k_offset, is_causal)
+    cv = lambda x, like: torch.zeros_like(like) if x is None else x.detach().to(dtype)
+    q, k, v, dO = (x.detach().to(dtype) for x in (q, k, v, dO))
+    uQ, uK, uV = cv(uQ, q), cv(uK, k), cv(uV, v)
+    zq = lambda: torch.zeros(B, Hq, Nq, D, dtype=dtype)
+    zk = lambda: torch.zeros(B, Hkv, Nk, D, dtype=dtype)
+    zs = lambda: torch.zeros(B, Hq, Nq, dtype=dtype)
+    out, dQ, Qbar, dObar = zq(), zq(), zq(), zq()
+    dK, dV, Kbar, Vbar = zk(), zk(), zk(), zk()
+    lse, delta, alpha, ecirc = zs(), zs(), zs(), zs()
+    kj = torch.arange(Nk) + int(k_offset)
+    for b in range(B):
+        for h in range(Hq):
+            hk = h // G
+            K_, V_, uK_, uV_ = k[b, hk], v[b, hk], uK[b, hk], uV[b, hk]
+            for r0 in range(0, Nq, row_block):
+                r1 = min(Nq, r0 + row_block)
+                Q_, dO_, uQ_ = q[b, h, r0:r1], dO[b, h, r0:r1], uQ[b, h, r0:r1]
+                if is_causal:
+                    dist = (torch.arange(r0, r1) + int(q_offset))[:, None] - kj[None, :]
+                    mask = dist >= 0
+                    if window_size:
+                        mask &= dist < int(window_size)
+                else:
+                    mask = torch.ones(r1 - r0, Nk, dtype=torch.bool)
+                S = (Q_ @ K_.T) * t
+                S = torch.where(mask, S, torch.full_like(S, -math.inf))
+                m = S.max(dim=-1, keepdim=True).values
+                has = torch.isfinite(m)
+                m = torch.where(has, m, torch.zeros_like(m))
+                e = torch.exp(S - m)
+                l = e.sum(-1, keepdim=True)
+                P = torch.where(has, e / torch.where(has, l, torch.ones_like(l)), torch.zeros_like(e))
+                L = torch.where(has, m + torch.log(torch.where(has, l, torch.ones_like(l))),
+                                torch.full_like(m, -math.inf)).squeeze(-1)
+                O_ = P @ V_
+                dl = (dO_ * O_).sum(-1)
+                dPs = dO_ @ V_.T - dl[:, None]
+                dS = P * dPs
+                dQ_ = t * (dS @ K_)
+                F = t * (uQ_ @ K_.T + Q_ @ uK_.T)
+                C = dO_ @ uV_.T
+                al = (P * F).sum(-1)
+                T = C + F * dPs
+                ec = (P * T).sum(-1)
+                Sbar = P * (T - al[:, None] * dPs - ec[:, None])
+                out[b, h, r0:r1], lse[b, h, r0:r1], delta[b, h, r0:r1] = O_, L, dl
+                alpha[b, h, r0:r1], ecirc[b, h, r0:r1], dQ[b, h, r0:r1] = al, ec, dQ_
+                dObar[b, h, r0:r1] = P @ uV_ + (P * F) @ V_ - al[:, None] * O_
+                Qbar[b, h, r0:r1] = t * ((P * T) @ K_ + dS @ uK_ - ec[:, None] * (P @ K_)) - al[:, None] * dQ_
+                dK[b, hk] += t * (dS.T @ Q_)
+                dV[b, hk] += P.T @ dO_
+                Kbar[b, hk] += t * (Sbar.T @ Q_ + dS.T @ uQ_)
+                Vbar[b, hk] += (P * (F - al[:, None])).T @ dO_
+    return DenseBoB(out=out, lse=lse, delta=delta, dQ=dQ, dK=dK, dV=dV, alpha=alpha, ecirc=ecirc,
+                    Qbar=Qbar, Kbar=Kbar, Vbar=Vbar, dObar=dObar)
+
+
 # --------------------------------------------------------------------------------------
 # the benchmark's loss chain
 # --------------------------------------------------------------------------------------
-def loss_chain(op, q, k, v, *, fp32_losses=False, hvp_directions=None, **kwargs):
+def loss_chain(op, q, k, v, *, fp32_losses=False, hvp_directions=None, mean_counts=None, **kwargs):
     """L1 = mean(out^2); first grads with create_graph; L2 = sum of mean(grad^2); second grads.
 
     Because dO depends on `out`, the second differentiation re-enters the first backward:
     (ddq, ddk, ddv) = (Qbar, Kbar, Vbar) + first_backward(cotangent = (2/numel) dObar).
     With `hvp_directions` = (gq, gk, gv) also returns the Hessian-vector product of L1.
+    `mean_counts` = (numel of out and q, numel of k) replaces the means' denominators: a shard of
+    (batch, KV head) units evaluated with the FULL tensors' element counts gives exactly the
+    full chain's gradients for that shard (heads do not interact).
     """
     q, k, v = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
     out = op(q, k, v, **kwargs)
     up = (lambda t: t.float()) if fp32_losses else (lambda t: t)
-    L1 = up(out).square().mean()
+    if mean_counts is None:
+        mean = lambda t, which: up(t).square().mean()
+    else:
+        mean = lambda t, which: up(t).square().sum() / mean_counts[which]
+    L1 = mean(out, 0)
     dq, dk, dv = torch.autograd.grad(L1, (q, k, v), create_graph=True)
-    L2 = up(dq).square().mean() + up(dk).square().mean() + up(dv).square().mean()
+    L2 = mean(dq, 0) + mean(dk, 1) + mean(dv, 1)
     want_hvp = hvp_directions is not None
     ddq, ddk, ddv = torch.autograd.grad(L2, (q, k, v), retain_graph=want_hvp)
     res = {"out": out.detach(), "dq": dq.detach(), "dk": dk.detach(), "dv": dv.detach(),

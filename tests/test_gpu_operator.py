@@ -177,3 +177,38 @@ def test_second_backward_is_linear_in_the_tangents_at_full_size():
     for n in O.OUTPUT_NAMES:
         m = O.error_metrics(got[n], getattr(ref, n))
         assert m["l2_rel"] < 6e-3 and m["max_abs_rel"] < 3e-2, (n, m)
+
+
+def test_config2_loss_chain_and_hessian_vector_product_through_the_operator():
+    """bf16 GQA B=1 Hq=32 Hkv=8 S=4096 D=64 causal through `bob.sdpa_bob`: the literal two-level chain
+    (L1 = mean(out^2), L2 = sum of mean(grad^2)) AND the Hessian-vector product of L1 with N(0,1)
+    directions (the pattern of the reference's examples/hessian_vector_product.py:54-61), against
+    the fp64 oracle evaluated KV group by KV group with the full tensors' element counts in the
+    means.  Values are ~1e-17, so errors are relative; the bf16 loss arithmetic (squares and means of
+    bf16 tensors) is part of what is compared."""
+    B, Hq, Hkv, N, D = 1, 32, 8, 4096, 64
+    G = Hq // Hkv
+    q, k, v = O.seeded_inputs(2, (B, Hq, N, D), (B, Hkv, N, D), BF16)
+    gq, gk, gv = O.seeded_inputs(1002, (B, Hq, N, D), (B, Hkv, N, D), BF16)
+    got = O.loss_chain(bob.sdpa_bob, q.cuda(), k.cuda(), v.cuda(), hvp_directions=(gq.cuda(), gk.cuda(), gv.cuda()),
+                       is_causal=True)
+    got = {n: t.float().cpu() for n, t in got.items()}
+    counts = (q.numel(), k.numel())
+    worst = {}
+    for hk in range(Hkv):
+        hs, ks = slice(hk * G, hk * G + G), slice(hk, hk + 1)
+        ref = O.loss_chain(O.attention_dense, q[:, hs].double(), k[:, ks].double(), v[:, ks].double(),
+                           hvp_directions=(gq[:, hs].double(), gk[:, ks].double(), gv[:, ks].double()),
+                           mean_counts=counts, is_causal=True)
+        for n in ("out", "dq", "ddq", "hvq"):
+            m = O.error_metrics(got[n][:, hs], ref[n])
+            worst[n] = max(worst.get(n, 0.0), m["l2_rel"])
+        for n in ("dk", "dv", "ddk", "ddv", "hvk", "hvv"):
+            m = O.error_metrics(got[n][:, ks], ref[n])
+            worst[n] = max(worst.get(n, 0.0), m["l2_rel"])
+    # first-order quantities carry one level of bf16 rounding, second-order ones two levels plus
+    # the bf16 loss arithmetic between them
+    for n in ("out", "dq", "dk", "dv"):
+        assert worst[n] < 8e-3, (n, worst)
+    for n in ("ddq", "ddk", "ddv", "hvq", "hvk", "hvv"):
+        assert worst[n] < 2e-2, (n, worst)

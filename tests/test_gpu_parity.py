@@ -245,5 +245,66 @@ def test_c_abi_rejects_bad_arguments_on_the_host():
     assert call() == -5
     g.q_strides[2] = 64
     assert lib.bob_sm100_fwd(ctypes.byref(g), vp(t), vp(t), vp(t), vp(t), vp(lse), None, None) == -6
+    # misaligned pointers are refused on the host instead of faulting on the device: inputs read by
+    # TMA, results written with 16-byte stores, pk read as float4 (16 bytes), fp32 statistics (4 bytes)
+    off = lambda x, n: ctypes.c_void_p(x.data_ptr() + n)
+    assert lib.bob_sm100_fwd(ctypes.byref(g), off(t, 2), vp(t), vp(t), vp(t), vp(lse), vp(ws), None) == -10
+    assert lib.bob_sm100_fwd(ctypes.byref(g), vp(t), vp(t), vp(t), off(t, 8), vp(lse), vp(ws), None) == -10
+    assert lib.bob_sm100_fwd(ctypes.byref(g), vp(t), vp(t), vp(t), vp(t), off(lse, 2), vp(ws), None) == -10
+    for f in (g.out_strides, g.do_strides, g.dq_strides, g.uq_strides, g.uk_strides, g.uv_strides):
+        f[0], f[1], f[2] = 2 * 64 * 64, 64 * 64, 64
+    pk = torch.zeros(1, 2, 64, 64, device="cuda")
+    bwd1 = lambda dq, dk, dv, dl, pk_: lib.bob_sm100_bwd1(ctypes.byref(g), vp(t), vp(t), vp(t), vp(t), vp(lse), vp(t),
+                                                          dq, dk, dv, dl, pk_, vp(ws), None)
+    assert bwd1(off(t, 8), vp(t), vp(t), vp(lse), vp(pk)) == -10
+    assert bwd1(vp(t), vp(t), off(t, 4), vp(lse), vp(pk)) == -10
+    assert bwd1(vp(t), vp(t), vp(t), off(lse, 1), vp(pk)) == -10
+    assert bwd1(vp(t), vp(t), vp(t), vp(lse), off(pk, 8)) == -10
+    ws2 = torch.zeros(lib.bob_sm100_workspace_bytes(_lib.STAGE_BWD2, ctypes.byref(g)), dtype=torch.uint8, device="cuda")
+    bwd2 = lambda qb, kb, vb, dob, pk_: lib.bob_sm100_bwd2(ctypes.byref(g), vp(t), vp(t), vp(t), vp(t), vp(lse), vp(lse),
+                                                           pk_, vp(t), vp(t), vp(t), vp(t), vp(t), qb, kb, vb, dob,
+                                                           vp(ws2), None)
+    assert bwd2(vp(t), vp(t), vp(t), off(t, 8), vp(pk)) == -10
+    assert bwd2(vp(t), off(t, 2), vp(t), vp(t), vp(pk)) == -10
+    assert bwd2(vp(t), vp(t), vp(t), vp(t), off(pk, 4)) == -10
+    assert lib.bob_sm100_bwd2_part(4, ctypes.byref(g), *([vp(t)] * 4), vp(lse), vp(lse), vp(pk), *([vp(t)] * 9),
+                                   vp(ws2), None) == -2
     torch.cuda.synchronize()
     assert b"stride" in lib.bob_sm100_error_string(-5)
+    assert b"aligned" in lib.bob_sm100_error_string(-10)
+
+
+@pytest.mark.parametrize("D", [16, 48, 80, 96, 112])
+def test_head_dims_between_the_operator_s_three(D):
+    """The C ABI takes any head dim that is a multiple of 16 up to 128 (the operator itself admits
+    32, 64 and 128): TMA zero-fills the padding columns and the stores skip them."""
+    B, Hq, Hkv, N = 1, 4, 2, 150
+    q, k, v, dO, uQ = O.seeded_inputs(70 + D, (B, Hq, N, D), (B, Hkv, N, D), BF16, n_extra_q=2)
+    uK, uV = O.seeded_inputs(170 + D, (B, Hq, N, D), (B, Hkv, N, D), BF16)[1:]
+    geom = _geom(N, N, is_causal=True)
+    ref = O.bob_closed_form(q, k, v, dO, uQ, uK, uV, **geom)
+    got, lse, _ = _run_kernels(q, k, v, dO, uQ, uK, uV, geom)
+    torch.testing.assert_close(lse.cpu().double(), ref.lse, rtol=1e-5, atol=1e-5)
+    for n in O.OUTPUT_NAMES:
+        _check(f"d{D}:{n}", got[n], getattr(ref, n), BF16)
+
+
+def test_a_give_up_is_visible_without_synchronising_per_call():
+    """A kernel that gives up on a bounded wait also writes its code to a page-locked host word; the
+    next call on the device (or `ops.check_device_status`) raises.  The run-out is the library's own
+    self-test kernel (a wait that nothing completes), nothing faults."""
+    lib = _lib.load()
+    dev = torch.cuda.current_device()
+    t = torch.zeros(1, 2, 64, 64, dtype=BF16, device="cuda")
+    geom = _geom(64, 64, is_causal=True)
+    ops.attention_forward(t, t, t, **geom)                  # sets up the device's status word
+    torch.cuda.synchronize()
+    assert lib.bob_sm100_last_status(dev) == 0
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.bob_sm100_timeout_selftest(st.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert st.item() == 77
+    with pytest.raises(_lib.BobSm100Error, match="77"):
+        ops.check_device_status()
+    assert lib.bob_sm100_last_status(dev) == 0              # reading clears it
+    ops.attention_forward(t, t, t, **geom)                  # and later calls are unaffected

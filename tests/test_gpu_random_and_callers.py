@@ -90,6 +90,47 @@ def test_flash_attn_layout_adapter_reads_bnhd_storage_in_place():
     assert O.error_metrics(win, ref)["l2_rel"] < 6e-3
 
 
+def test_hf_attention_interface_against_the_oracle():
+    """The Hugging Face attention-interface signature (reference: examples/huggingface_backend.py:29-61):
+    grouped heads through `num_key_value_groups`-style shapes, a sliding window, and a single-token
+    decode step over a cache (right-aligned, so every cached key - or the last `sliding_window` of
+    them - is visible).  Output layout [B, N, H, D], contiguous."""
+    g = torch.Generator().manual_seed(9)
+    r = lambda *s: torch.randn(*s, generator=g).to(BF16)
+
+    class _Module:
+        is_causal = True
+
+    # grouped heads, prefill
+    q, k, v = r(2, 8, 150, 64), r(2, 2, 150, 64), r(2, 2, 150, 64)
+    out, w = adapters.hf_attention_interface(_Module(), q.cuda(), k.cuda(), v.cuda(), None, scaling=0.11)
+    assert w is None and out.shape == (2, 150, 8, 64) and out.is_contiguous()
+    ref = O.attention_dense(q.double(), k.double(), v.double(), is_causal=True, scale=0.11).transpose(1, 2)
+    assert O.error_metrics(out, ref)["l2_rel"] < 6e-3
+    # sliding window, prefill (multi-head: the reference supports windows without grouping)
+    q, k, v = r(1, 4, 300, 64), r(1, 4, 300, 64), r(1, 4, 300, 64)
+    out, _ = adapters.hf_attention_interface(_Module(), q.cuda(), k.cuda(), v.cuda(), None, sliding_window=64)
+    ref = O.attention_dense(q.double(), k.double(), v.double(), is_causal=True, window_size=64).transpose(1, 2)
+    assert O.error_metrics(out, ref)["l2_rel"] < 6e-3
+    # single-token decode over a cache of 257 keys, with and without a window
+    q, k, v = r(2, 4, 1, 64), r(2, 4, 257, 64), r(2, 4, 257, 64)
+    for window in (0, 100):
+        out, _ = adapters.hf_attention_interface(_Module(), q.cuda(), k.cuda(), v.cuda(), None,
+                                                 sliding_window=window or None)
+        assert out.shape == (2, 1, 4, 64)
+        ref = O.attention_dense(q.double(), k.double(), v.double(), is_causal=True, window_size=window,
+                                q_offset=256, k_offset=0).transpose(1, 2)
+        assert O.error_metrics(out, ref)["l2_rel"] < 6e-3, window
+    # second order through the adapter: gradients flow through the transposed, contiguous output
+    q, k, v = (t.cuda().requires_grad_(True) for t in (r(1, 4, 96, 64), r(1, 2, 96, 64), r(1, 2, 96, 64)))
+    out, _ = adapters.hf_attention_interface(_Module(), q, k, v, None)
+    first = torch.autograd.grad(out.float().square().mean(), (q, k, v), create_graph=True)
+    second = torch.autograd.grad(sum(f.float().square().sum() for f in first), (q, k, v))
+    assert all(torch.isfinite(t.float()).all() and t.abs().max() > 0 for t in second)
+    with pytest.raises(NotImplementedError, match="padded"):
+        adapters.hf_attention_interface(_Module(), q, k, v, torch.zeros(1, 1, 96, 96, device="cuda"))
+
+
 class _Block(torch.nn.Module):
     def __init__(self, dim, heads, kv_heads, attend):
         super().__init__()

@@ -126,3 +126,39 @@ def test_unmasked_pair_count():
     assert O.unmasked_pairs(128, 512, is_causal=True, window_size=256, q_offset=1000, k_offset=616) == 32768
     m = O.valid_mask(13, 29, is_causal=True, window_size=5, q_offset=20, k_offset=3)
     assert int(m.sum()) == O.unmasked_pairs(13, 29, is_causal=True, window_size=5, q_offset=20, k_offset=3)
+
+
+def test_streamed_closed_form_equals_the_dense_closed_form():
+    """The row-blocked, head-by-head evaluation used for the largest configuration is the same
+    function as the dense closed form (which is pinned against the reference above)."""
+    cases = [((2, 4, 70, 16), (2, 2, 70, 16), dict(is_causal=True)),
+             ((1, 2, 33, 16), (1, 1, 90, 16), dict(is_causal=True, window_size=20)),
+             ((1, 3, 40, 8), (1, 3, 40, 8), dict()),
+             ((1, 2, 96, 16), (1, 2, 64, 16), dict(is_causal=True, q_offset=0, k_offset=40))]
+    for qs, ks, kw in cases:
+        q, k, v, dO, uQ = O.seeded_inputs(1, qs, ks, torch.float64, n_extra_q=2)
+        uK, uV = O.seeded_inputs(2, qs, ks, torch.float64)[1:]
+        a = O.bob_closed_form(q, k, v, dO, uQ, uK, uV, **kw)
+        b = O.bob_closed_form_streamed(q, k, v, dO, uQ, uK, uV, row_block=16, **kw)
+        for n in O.OUTPUT_NAMES + ("alpha", "ecirc", "delta"):
+            torch.testing.assert_close(getattr(b, n), getattr(a, n), rtol=1e-11, atol=1e-11)
+        fin = torch.isfinite(a.lse)
+        assert torch.equal(torch.isfinite(b.lse), fin)
+        torch.testing.assert_close(b.lse[fin], a.lse[fin], rtol=1e-12, atol=1e-12)
+
+
+def test_sharded_loss_chain_with_global_mean_counts_equals_the_full_chain():
+    """Evaluating the benchmark's loss chain on one KV group with the FULL tensors' element counts in
+    the means gives that group's slice of the full chain, Hessian-vector product included."""
+    q, k, v = O.seeded_inputs(7, (1, 4, 24, 8), (1, 2, 24, 8), torch.float64)
+    gq, gk, gv = O.seeded_inputs(8, (1, 4, 24, 8), (1, 2, 24, 8), torch.float64)
+    full = O.loss_chain(O.attention_dense, q, k, v, hvp_directions=(gq, gk, gv), is_causal=True)
+    for hk in range(2):
+        hs = slice(2 * hk, 2 * hk + 2)
+        part = O.loss_chain(O.attention_dense, q[:, hs], k[:, hk:hk + 1], v[:, hk:hk + 1],
+                            hvp_directions=(gq[:, hs], gk[:, hk:hk + 1], gv[:, hk:hk + 1]),
+                            mean_counts=(q.numel(), k.numel()), is_causal=True)
+        for n in ("ddq", "hvq", "dq"):
+            torch.testing.assert_close(part[n], full[n][:, hs], rtol=1e-10, atol=1e-18)
+        for n in ("ddk", "ddv", "hvk", "hvv", "dk", "dv"):
+            torch.testing.assert_close(part[n], full[n][:, hk:hk + 1], rtol=1e-10, atol=1e-18)

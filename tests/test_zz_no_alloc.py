@@ -70,6 +70,7 @@ def test_noalloc_second_backward_matches_regular_entry_point_twice():
         assert _call(lib, "bob_sm100_bwd2_noalloc", g, t, second) == 0    # same stream share the scratch
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert lib.bob_sm100_noalloc_read_status(torch.cuda.current_device(), None) == 0
         for got in (first, second):
             for name, a, b in zip(("Qbar", "Kbar", "Vbar", "dObar"), got, ref):
                 assert torch.isfinite(a.float()).all(), (round_, name)
