@@ -194,9 +194,8 @@ def cpu_reference_sample(wl: dict, steps: int, warmup: int, budget_s: float) -> 
     n_pass = steps + warmup
     if REF_DIR.exists() and REF_RUNNER.exists():
         base = ["--mode", "cpu", "--seq", str(wl["N"]), "--dim", str(wl["D"]), "--threads", str(threads)]
-        t0 = time.perf_counter()
-        _run_child([str(REF_RUNNER), *base, "--heads", "1", "--steps", "1", "--warmup", "0"], 900)
-        per_head = max(1e-3, time.perf_counter() - t0)        # whole child: start-up, graph building, one pass
+        probe = _run_child([str(REF_RUNNER), *base, "--heads", "1", "--steps", "1", "--warmup", "0"], 900)
+        per_head = max(1e-3, 3.0 * probe["seconds"][0])       # a timed pass plus the untimed graph building before it
         heads = max(1, min(G, int(budget_s / (per_head * n_pass))))
         kv = max(1, min(Hkv, int(budget_s / (per_head * G * n_pass)))) if heads == G else 1
         r = _run_child([str(REF_RUNNER), *base, "--heads", str(heads), "--kv-heads", str(kv), "--steps", str(steps),

@@ -3,6 +3,7 @@
 #include "sweep.cuh"
 #include "tmap.h"
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdlib>
@@ -80,6 +81,42 @@ static int sm_count(int device) {
     return cache[device];
 }
 
+// Column-owned kernels: number of TN-wide query tiles that the 128 keys of own tile `own_tile` sweep
+// (the host's copy of the kernel's item decoding: same clipping of the causal / window range).
+static int col_sweep_tiles(const bob_sm100_geom* g, long long doff, int own_tile, int TN) {
+    const long long own0 = 128LL * own_tile, own_last = std::min<long long>(own0 + 127, g->Nk - 1);
+    long long lo = 0, hi = g->Nq;
+    if (g->is_causal) {
+        lo = std::max<long long>(0, own0 - doff);
+        if (g->window > 0) hi = std::min<long long>(g->Nq, own_last - doff + g->window);
+    }
+    if (hi <= lo) return 0;
+    return (int)((hi + TN - 1) / TN - lo / TN);
+}
+
+// Even split of a persistent column-owned launch over `ctas` CTAs: tile pairs per CTA, or 0 when the
+// split does not apply (too little work per CTA to pay for the cut items' extra epilogues, or a list
+// too long for 32-bit positions).
+static int even_split_span(const bob_sm100_geom* g, long long doff, int TN, int ctas) {
+    const int n_own_tiles = (g->Nk + 127) / 128;
+    const long long per_rank = (long long)g->Hkv * g->B, G = g->Hq / g->Hkv;
+    long long total = 0;
+    for (int r = 0; r < n_own_tiles; ++r) total += (long long)col_sweep_tiles(g, doff, r, TN) * G * per_rank;
+    if (total <= 0 || total >= (1LL << 30)) return 0;
+    const long long span = (total + ctas - 1) / ctas;
+    return span >= 32 ? (int)span : 0;
+}
+
+static size_t even_split_flag_bytes(const bob_sm100_geom* g) {
+    return round256((size_t)((g->Nk + 127) / 128) * g->Hkv * g->B * sizeof(int));
+}
+static size_t even_split_park_bytes(int ctas) { return (size_t)ctas * 2 * 2 * 128 * 64 * sizeof(float); }
+
+// Whether a column-owned launch of this geometry is persistent (one CTA per SM taking many items).
+static bool col_launch_is_persistent(const bob_sm100_geom* g, int sms) {
+    return g->D <= 64 && (long long)((g->Nk + 127) / 128) * g->Hkv * g->B > sms;
+}
+
 struct TensorArg {
     const void* ptr;
     const int64_t* strides;   // batch, head, row
@@ -139,8 +176,16 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
     // alternating assignment, so there the grid covers every item and each CTA runs a single round.
     const bool persistent = (DPAD == 64) && items > sms;
     dim3 grid((unsigned)(persistent ? sms : items), 1, 1);
-    // Persistent CTAs take items, longest first, from a counter in the status block (zeroed with it).
+    // Persistent CTAs take items, longest first, from a counter in the status block (zeroed with it);
+    // column-owned ones with a parking area instead split the item list evenly (see the kernel).
     prm.work_counter = persistent ? prm.status + kCounterWord0 + counter_slot : nullptr;
+    prm.sk_span = 0;
+    if (MT::COL && persistent && prm.sk_park && prm.sk_flags) {
+        prm.sk_span = even_split_span(g, prm.delta_off, TN, (int)grid.x);
+        if (prm.sk_span > 0 &&
+            cudaMemsetAsync(prm.sk_flags, 0, even_split_flag_bytes(g), stream) != cudaSuccess)
+            return kErrLaunch;
+    }
     kernel<<<grid, CFG::NTHREADS, CFG::SMEM_BYTES, stream>>>(prm);
     return cudaGetLastError() == cudaSuccess ? 0 : kErrLaunch;
 }
@@ -263,6 +308,7 @@ extern "C" const char* bob_sm100_error_string(int code) {
         case -12: return "problem too large for the built-in scratch (B*Hq*Nq > 1048576 rows)";
         case -101: return "tensor base address must be 16-byte aligned";
         case -102: return "tensor strides unusable for TMA";
+        case 77: return "device: the self-test's wait ran out (as it is meant to)";
         case kStatusTimeoutLoad: return "device: a wait for a TMA load ran out";
         case kStatusTimeoutMma: return "device: a wait in the MMA issuer ran out";
         case kStatusTimeoutPw: return "device: a wait in the pointwise threads ran out";
@@ -270,11 +316,18 @@ extern "C" const char* bob_sm100_error_string(int code) {
     }
 }
 
+// Bytes of the even-split area (flags, then parked partials) a stage's column-owned kernel may use.
+static size_t even_split_bytes(const bob_sm100_geom* g) {
+    const int sms = sm_count(g->device);
+    if (sms <= 0 || !col_launch_is_persistent(g, sms)) return 0;
+    return even_split_flag_bytes(g) + even_split_park_bytes(sms);
+}
+
 extern "C" size_t bob_sm100_workspace_bytes(int stage, const bob_sm100_geom* g) {
-    if (!g) return 0;
+    if (!g || g->B <= 0 || g->Hq <= 0 || g->Hkv <= 0 || g->Nq <= 0 || g->Nk <= 0) return 0;
     size_t bytes = kStatusBlock;
-    if (stage == BOB_SM100_STAGE_BWD2)
-        bytes += 2 * round256(static_cast<size_t>(g->B) * g->Hq * g->Nq * sizeof(float));
+    if (stage == BOB_SM100_STAGE_BWD2) bytes = bwd2_workspace_bytes_unsplit(g);
+    if (stage == BOB_SM100_STAGE_BWD1 || stage == BOB_SM100_STAGE_BWD2) bytes += even_split_bytes(g);
     return bytes;
 }
 
@@ -365,6 +418,10 @@ extern "C" int bob_sm100_bwd1(const bob_sm100_geom* g, const void* q, const void
     if (rc) return rc;
     p.res0 = dK;
     p.res1 = dV;
+    if (even_split_bytes(g)) {
+        p.sk_flags = reinterpret_cast<int*>(static_cast<char*>(workspace) + kStatusBlock);
+        p.sk_park = reinterpret_cast<float*>(static_cast<char*>(workspace) + kStatusBlock + even_split_flag_bytes(g));
+    }
     return dispatch_dtype<kBwd1Col>(g, p, t, s, 1); // dK and dV (reads delta)
 }
 
@@ -372,7 +429,6 @@ int bob::bwd2_impl(const bob_sm100_geom* g, const void* q, const void* k, const 
                    const float* lse, const float* delta, const float* pk, const void* dO, const void* dQ,
                    const void* uQ, const void* uK, const void* uV, void* Qbar, void* Kbar, void* Vbar,
                    void* dObar, void* workspace, void* stream, int* sticky, int part, bool allow_split) {
-    (void)allow_split;
     int rc = check_geom(g);
     if (rc) return rc;
     if (!q || !k || !v || !out || !lse || !delta || !pk || !dO || !dQ || !Qbar || !Kbar || !Vbar || !dObar)
@@ -418,6 +474,11 @@ int bob::bwd2_impl(const bob_sm100_geom* g, const void* q, const void* k, const 
     if (part & kPartCol) {
         p.res0 = Kbar;
         p.res1 = Vbar;
+        if (allow_split && even_split_bytes(g)) {
+            char* area = static_cast<char*>(workspace) + bwd2_workspace_bytes_unsplit(g);
+            p.sk_flags = reinterpret_cast<int*>(area);
+            p.sk_park = reinterpret_cast<float*>(area + even_split_flag_bytes(g));
+        }
         rc = dispatch_dtype<kBwd2Col>(g, p, t, s, 1);   // Kbar, Vbar (reads alpha, ecirc)
     }
     return rc;

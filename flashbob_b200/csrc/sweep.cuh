@@ -75,6 +75,13 @@ struct SweepParams {
     int* status;
     int* sticky;                  // optional second word that a CTA giving up also writes (host-visible memory)
     int* work_counter;            // persistent launches: next work item (zeroed by the host); null: one item per CTA
+    // Even split (column-owned modes, persistent launches): every CTA takes `sk_span` consecutive tile
+    // pairs of the item list, cutting items where its span ends.  The pieces of a cut item park their
+    // fp32 partial results in `sk_park` (two slots per CTA) and count themselves in `sk_flags[item]`
+    // (zeroed by the host); the last piece to finish adds the parked partials and stores the result.
+    int sk_span;                  // 0: off
+    float* sk_park;
+    int* sk_flags;
     long long* phase_cycles;      // optional cycle counters per pipeline phase (builds with BOB_PHASE_TIMERS)
 };
 
@@ -167,7 +174,7 @@ struct SweepConfig {
     static constexpr int RING = 4;                                              // work items announced ahead
     static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG + 2 * RING;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag, item ring
-    static constexpr int OFF_IO = (OFF_MISC + 16 + 4 * RING + 127) & ~127;      // staged epilogue operands
+    static constexpr int OFF_IO = (OFF_MISC + 16 + 32 * RING + 127) & ~127;     // staged epilogue operands
     static constexpr int SMEM_BYTES = OFF_IO + IO_BYTES + 1024;                 // + alignment slack
     static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
 };
@@ -294,6 +301,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     // predicated on values only known at run time.
     const bool has_uq = ALLT || p.has_uq != 0, has_uk = ALLT || p.has_uk != 0, has_uv = ALLT || p.has_uv != 0;
     struct Item { int own0, head, batch, kv_head, t_lo, t_hi, T, total; };
+    // What the ring announces: an item, or a piece of one (tile pairs [lin0, lin0 + len) of its sweep,
+    // counted head by head); part != 0 marks a piece of a cut item, whose list position starts at s_item.
+    struct Work { int item, lin0, len, part, s_item; };
     auto decode = [&](int item) {
         Item w;
         const int tile_rank = item / per_rank;
@@ -327,10 +337,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     // shared memory; the MMA warp and the pointwise warps follow the ring.
     constexpr int RING = CFG::RING;
     volatile int* item_ring = reinterpret_cast<volatile int*>(sptr + CFG::OFF_MISC + 16);
-#define BOB_ITEM_LOCALS(w)                                                                         \
+#define BOB_ITEM_LOCALS(w, wk)                                                                     \
     const int own0 = (w).own0, head = (w).head, batch = (w).batch, kv_head = (w).kv_head;         \
-    const int t_lo = (w).t_lo, t_hi = (w).t_hi, T = (w).T, total = (w).total;                      \
-    (void)own0; (void)head; (void)batch; (void)kv_head; (void)t_lo; (void)t_hi; (void)T; (void)total;
+    const int t_lo = (w).t_lo, t_hi = (w).t_hi, T = (w).T;                                         \
+    const int total = (wk).len < 0 ? (w).total : (wk).len;          /* tile pairs of this piece */ \
+    const int lin0 = (wk).len < 0 ? 0 : (wk).lin0;                                                 \
+    (void)own0; (void)head; (void)batch; (void)kv_head; (void)t_lo; (void)t_hi; (void)T; (void)total; (void)lin0;
 
     // ---- set-up ------------------------------------------------------------------------------
     if (tid == 0) {
@@ -367,17 +379,22 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         atomicCAS(p.status, 0, code);
         if (p.sticky) { *reinterpret_cast<volatile int*>(p.sticky) = code; __threadfence_system(); }
     };
-    // Followers of the item ring: the k-th announced item (-1: none left; -2: the wait ran out).
-    auto follow_ring = [&](int k) -> int {
+    // Followers of the item ring: the k-th announced piece of work (item -1: none left; -2: the wait ran out).
+    auto follow_ring = [&](int k) -> Work {
         const int slot = k % RING;
-        if (!__all_sync(0xffffffffu, mbar_wait(bar_item_full(slot), (k / RING) & 1))) return -2;
-        // every lane reads the same word; the broadcast tells the compiler that the value (and all
-        // the loop bounds and addresses derived from it) is uniform across the warp
-        const int item = __shfl_sync(0xffffffffu, item_ring[slot], 0);
+        Work wk = {-2, 0, -1, 0, 0};
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_item_full(slot), (k / RING) & 1))) return wk;
+        // every lane reads the same words; the broadcast tells the compiler that the values (and all
+        // the loop bounds and addresses derived from them) are uniform across the warp
+        volatile int* e = item_ring + 8 * slot;
+        wk.item = __shfl_sync(0xffffffffu, e[0], 0);
+        wk.lin0 = __shfl_sync(0xffffffffu, e[1], 0);
+        wk.len = __shfl_sync(0xffffffffu, e[2], 0);
+        wk.part = __shfl_sync(0xffffffffu, e[3], 0);
+        wk.s_item = __shfl_sync(0xffffffffu, e[4], 0);
         if (lane == 0) mbar_arrive(bar_item_empty(slot));
-        return item;
+        return wk;
     };
-    auto aborted = [&]() { return misc[1] != 0; };
 
     auto has_tensor = [&](int t) {
         return t == kTUQ ? has_uq : (t == kTUK ? has_uk : (t == kTUV ? has_uv : true));
@@ -398,6 +415,24 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         int s = 0, round = 0;                    // pipeline stage of tile `cnt`, and cnt / NSTAGE
         int n_live = 0;                          // items with at least one tile started so far
         bool alive = true;
+        // Even split: this CTA's span [sk_pos, sk_end) of the item list, counted in tile pairs.  The list
+        // is ordered by tile rank; the per_rank items of a rank are equally long (sk_len tile pairs each)
+        // and the rank's first item starts at list position sk_rank0.
+        const bool even_split = COL && p.sk_span > 0;
+        long long sk_pos = 0, sk_end = 0, sk_rank0 = 0;
+        int sk_rank = 0, sk_len = 0;
+        int z_rank = 0, z_idx = 0, z_count = 0;             // cursor over the items that have no tile pair at all
+        auto rank_len = [&](int r) { return decode(r * per_rank).T * n_outer; };
+        if (even_split) {
+            sk_pos = (long long)blockIdx.x * p.sk_span;
+            sk_end = sk_pos + p.sk_span;
+            for (sk_rank = 0; sk_rank < n_own_tiles; ++sk_rank) {
+                sk_len = rank_len(sk_rank);
+                const long long nxt = sk_rank0 + (long long)sk_len * per_rank;
+                if (sk_pos < nxt) break;
+                sk_rank0 = nxt;
+            }
+        }
         for (int k_item = 0; alive; ++k_item) {
             const int slot = k_item % RING;
             if (k_item >= RING &&
@@ -405,22 +440,50 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 if (lane == 0) give_up(kStatusTimeoutLoad);
                 break;
             }
-            int item = -1;
-            if (lane == 0) {
+            Work wk = {-1, 0, -1, 0, 0};
+            if (even_split) {
+                if (sk_rank < n_own_tiles && sk_pos < sk_end) {
+                    // the next piece of my span
+                    const int in_rank = (int)((sk_pos - sk_rank0) / sk_len);
+                    const long long s_item = sk_rank0 + (long long)in_rank * sk_len;
+                    wk.item = sk_rank * per_rank + in_rank;
+                    wk.lin0 = (int)(sk_pos - s_item);
+                    wk.len = (int)min(s_item + sk_len - sk_pos, sk_end - sk_pos);
+                    wk.part = (wk.len == sk_len) ? 0 : 1;
+                    wk.s_item = (int)s_item;
+                    sk_pos += wk.len;
+                    if (sk_pos == sk_rank0 + (long long)sk_len * per_rank) {     // the rank is used up
+                        sk_rank0 = sk_pos;
+                        do { ++sk_rank; sk_len = sk_rank < n_own_tiles ? rank_len(sk_rank) : 0; }
+                        while (sk_rank < n_own_tiles && sk_len == 0);
+                    }
+                } else {
+                    // my span is used up: the items without any tile pair (their results are zeros, written
+                    // by the pointwise threads) are dealt to the CTAs in turn
+                    while (z_rank < n_own_tiles && wk.item < 0) {
+                        if (rank_len(z_rank) != 0 || z_idx == per_rank) { ++z_rank; z_idx = 0; continue; }
+                        if (z_count % (int)gridDim.x == (int)blockIdx.x) { wk.item = z_rank * per_rank + z_idx; wk.len = 0; }
+                        ++z_idx; ++z_count;
+                    }
+                }
+            } else {
 #ifdef BOB_STATIC_ITEMS
-                if (p.work_counter) item = k_item * (int)gridDim.x + ((k_item & 1) ? ((int)gridDim.x - 1 - (int)blockIdx.x) : (int)blockIdx.x);
+                if (p.work_counter) wk.item = k_item * (int)gridDim.x + ((k_item & 1) ? ((int)gridDim.x - 1 - (int)blockIdx.x) : (int)blockIdx.x);
 #else
-                if (p.work_counter) item = atomicAdd(p.work_counter, 1);
+                if (p.work_counter) { if (lane == 0) wk.item = atomicAdd(p.work_counter, 1); wk.item = __shfl_sync(0xffffffffu, wk.item, 0); }
 #endif
-                else if (k_item == 0) item = (int)blockIdx.x;
-                if (item < 0 || item >= n_items) item = -1;
-                item_ring[slot] = item;
+                else if (k_item == 0) wk.item = (int)blockIdx.x;
+                if (wk.item < 0 || wk.item >= n_items) wk.item = -1;
+            }
+            if (lane == 0) {
+                volatile int* e = item_ring + 8 * slot;
+                e[0] = wk.item; e[1] = wk.lin0; e[2] = wk.len; e[3] = wk.part; e[4] = wk.s_item;
                 mbar_arrive(bar_item_full(slot));
             }
-            item = __shfl_sync(0xffffffffu, item, 0);
+            const int item = wk.item;
             if (item < 0) break;
             const Item w = decode(item);
-            BOB_ITEM_LOCALS(w)
+            BOB_ITEM_LOCALS(w, wk)
             if (total == 0) continue;
             if (n_live > 0) {
                 // the previous item's last products have finished reading its own tiles
@@ -446,7 +509,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 }
             }
             ++n_live;
-            int tile = t_lo, outer = 0;              // swept tile of iteration `it`, and it / T
+            int tile = t_lo + lin0 % T, outer = lin0 / T;     // swept tile of iteration `it`, and its head in the group (T > 0 here)
             for (int it = 0; it < total; ++it) {
                 bool go = true;
                 if (cnt >= NSTAGE) go = mbar_wait(bar_empty(s), (round - 1) & 1);
@@ -588,11 +651,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             int n_live = 0;                           // items with at least one tile finished so far
             bool ok = true;
             for (int k_item = 0; ok; ++k_item) {
-            const int item = follow_ring(k_item);
+            const Work wk = follow_ring(k_item);
+            const int item = wk.item;
             if (item == -2) give_up(kStatusTimeoutMma);
             if (item < 0) break;
             const Item w = decode(item);
-            BOB_ITEM_LOCALS(w)
+            BOB_ITEM_LOCALS(w, wk)
             if (total == 0) continue;
             ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
             if (!ok) give_up(kStatusTimeoutMma);
@@ -713,11 +777,12 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         BOB_PH_DECL
 
         for (int k_item = 0; ok; ++k_item) {
-            const int item = follow_ring(k_item);
+            const Work wk = follow_ring(k_item);
+            const int item = wk.item;
             if (item == -2) give_up(kStatusTimeoutPw);
             if (item < 0) break;
         const Item w = decode(item);
-        BOB_ITEM_LOCALS(w)
+        BOB_ITEM_LOCALS(w, wk)
         const int own_idx = own0 + row;
         const bool own_ok = own_idx < n_own;
         const long long row_stat = ((long long)batch * p.Hq + head) * p.Nq + own_idx;   // row-owned only
@@ -960,11 +1025,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 } else {
                     issue_loads(0, 0);
                 }
-#ifdef BOB_STORE_LATE
-                constexpr bool STORE_LATE = LOAD_ALL;    // all rounds' arithmetic first, then the wait and the stores
-#else
-                constexpr bool STORE_LATE = false;
-#endif
+                constexpr bool STORE_LATE = false;       // (all rounds' arithmetic before the wait and the stores: measured slower)
                 uint32_t wbuf[STORE_LATE ? R : 1][4][RW / 2];
                 auto store_round = [&](int half) {
                     const uint32_t dst = op_taddr + (RW / 2) * half;     // RW / 2 packed words per round
@@ -1086,30 +1147,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                             }
                         }
                     };
-#ifdef BOB_SWP
-                    {
-                        Grp cur = exps(0);
-                        #pragma unroll
-                        for (int c4 = 0; c4 < RW / 4; ++c4) {
-                            Grp nxt = cur;
-                            if (c4 + 1 < RW / 4) {
-                                nxt = exps(c4 + 1);
-                                // keeps the order: these exponentials are issued before the products below
-                                asm volatile("" : "+f"(nxt.pr[0].x), "+f"(nxt.pr[0].y), "+f"(nxt.pr[1].x), "+f"(nxt.pr[1].y));
-                            }
-                            math(c4, cur);
-                            if (c4 + 2 < RW / 4) {
-                                // ... and the exponentials after the next ones not before these products
-                                const int cn = 4 * (c4 + 2);
-                                asm volatile("" : "+r"(w0[2 * c4 + 1]), "+f"(s_[cn]), "+f"(s_[cn + 1]), "+f"(s_[cn + 2]), "+f"(s_[cn + 3]));
-                            }
-                            cur = nxt;
-                        }
-                    }
-#else
                     #pragma unroll
                     for (int c4 = 0; c4 < RW / 4; ++c4) math(c4, exps(c4));
-#endif
                     if constexpr (!LOAD_ALL) {
                         if (half + 1 < R) issue_loads(half + 1, 0);
                     }
@@ -1163,7 +1202,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 }
                 if (hi > lo) { full_lo = (int)lo; full_hi = (int)hi; }
             }
-            int tile = t_lo, outer = 0;
+            int tile = t_lo + (T > 0 ? lin0 % T : 0), outer = T > 0 ? lin0 / T : 0;
             for (int it = 0; ok && it < total; ++it) {
                 if ((cnt + it) % NG == grp) {            // my group's turn
                     // is the whole 128 x TN tile pair unmasked and inside both tensors?  (uniform per CTA)
@@ -1256,6 +1295,65 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             bool released = false;
             if (EARLY && total > 0) { release_outputs(); released = true; }
             BOB_PH(10)
+            // A piece of a cut item (even split, column-owned modes): park my fp32 partial results,
+            // count this piece in, and only if it is the last of its item to finish, add the other
+            // pieces' parked partials and go on to store the result.  Nothing waits for anything: a
+            // piece is counted after its partials are globally visible.
+            bool store_results = true;
+            if constexpr (COL && EARLY) {
+                if (wk.part != 0 && ok) {
+                    const long long span = p.sk_span, s_item = wk.s_item;
+                    const int me = (int)blockIdx.x;
+                    const int c_first = (int)(s_item / span), c_last = (int)((s_item + w.total - 1) / span);
+                    auto slot_of = [&](int c) {          // a CTA's first piece parks in slot 0, a later one in slot 1
+                        return (c > c_first || s_item == (long long)c * span) ? 0 : 1;
+                    };
+                    auto park_at = [&](int c) {
+                        return p.sk_park + ((size_t)(2 * c + slot_of(c)) * 2 * 128 + row) * DPAD + (grp * NSPLIT + sp) * DC;
+                    };
+                    float* mine = park_at(me);
+                    #pragma unroll
+                    for (int ch = 0; ch < NCH; ++ch) {
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            reinterpret_cast<float4*>(mine + 16 * ch)[i] =
+                                make_float4(acc0[ch][4 * i], acc0[ch][4 * i + 1], acc0[ch][4 * i + 2], acc0[ch][4 * i + 3]);
+                            reinterpret_cast<float4*>(mine + 128 * DPAD + 16 * ch)[i] =
+                                make_float4(acc1[ch][4 * i], acc1[ch][4 * i + 1], acc1[ch][4 * i + 2], acc1[ch][4 * i + 3]);
+                        }
+                    }
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_pw_all);
+                    ok = pw_wait(bar_pw_all, pw_all_phase);
+                    pw_all_phase ^= 1u;
+                    int* xch = reinterpret_cast<int*>(red_buf);
+                    if (tid == 0) xch[0] = atomicAdd(p.sk_flags + item, 1);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_pw_all);
+                    ok = ok && pw_wait(bar_pw_all, pw_all_phase);
+                    pw_all_phase ^= 1u;
+                    store_results = ok && (xch[0] == c_last - c_first);
+                    if (store_results) {
+                        __threadfence();
+                        for (int c = c_first; c <= c_last; ++c) {
+                            if (c == me) continue;
+                            const float* other = park_at(c);
+                            #pragma unroll
+                            for (int ch = 0; ch < NCH; ++ch) {
+                                #pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float4 a = __ldcg(reinterpret_cast<const float4*>(other + 16 * ch) + i);
+                                    const float4 b = __ldcg(reinterpret_cast<const float4*>(other + 128 * DPAD + 16 * ch) + i);
+                                    acc0[ch][4 * i] += a.x; acc0[ch][4 * i + 1] += a.y; acc0[ch][4 * i + 2] += a.z; acc0[ch][4 * i + 3] += a.w;
+                                    acc1[ch][4 * i] += b.x; acc1[ch][4 * i + 1] += b.y; acc1[ch][4 * i + 2] += b.z; acc1[ch][4 * i + 3] += b.w;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (store_results) {
             #pragma unroll
             for (int c = 0; c < DC; c += 16) {
                 const int col = (grp * NSPLIT + sp) * DC + c;
@@ -1348,6 +1446,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     }
                 }
             }
+            }   // store_results
             if (total > 0 && !released) release_outputs();   // a thread with no column inside the head dim
         }
         if constexpr (CFG::STAGED_IO) {

@@ -1,0 +1,66 @@
+"""The stated floating-point bar: errors against fp64 no worse than the reference's own CUDA route's.
+
+The unmodified reference (installed under baseline/_ref) runs in a child process
+that imports nothing of this repository: its cuDNN forward / first backward and Triton second
+backward produce all eight outputs for seeded inputs; the kernels here produce them for the same
+inputs; both are compared with the fp64 oracle on one KV group.  Per output tensor this library's
+relative L2 error and its max-abs error must not exceed the reference route's (5 % slack for the
+max-abs figure, which is the error of one element out of a million).
+Skipped where baseline/_ref is absent or the reference's route does not run on the installed
+torch / triton (it pins older versions).
+"""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from flashbob_b200 import ops
+from oracle import bob_oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+RUNNER = ROOT / "baseline" / "run_reference.py"
+BF16 = torch.bfloat16
+
+
+def _reference_outputs(tmp_path, B, Hq, Hkv, N, D, seed, group):
+    if not (ROOT / "baseline" / "_ref" / "bob").exists():
+        pytest.skip("baseline/_ref is not installed")
+    out_file = tmp_path / "ref.pt"
+    res = subprocess.run([sys.executable, str(RUNNER), "--mode", "cuda", "--batch", str(B), "--hq", str(Hq),
+                          "--hkv", str(Hkv), "--seq", str(N), "--dim", str(D), "--seed", str(seed), "--group",
+                          str(group), "--save", str(out_file)], capture_output=True, text=True, timeout=900)
+    if res.returncode != 0:
+        pytest.skip("the reference's CUDA route does not run here: " + (res.stderr.strip().splitlines() or ["?"])[-1][:200])
+    return torch.load(out_file)["outputs"], json.loads(res.stdout.strip().splitlines()[-1])
+
+
+@pytest.mark.parametrize("shape", [(1, 32, 8, 4096, 64), (1, 8, 2, 2048, 128)], ids=["gqa_s4096_d64", "gqa_s2048_d128"])
+def test_errors_against_fp64_are_no_worse_than_the_reference_cuda_route(tmp_path, shape):
+    B, Hq, Hkv, N, D = shape
+    seed, group, G = 2, 1, Hq // Hkv
+    theirs, info = _reference_outputs(tmp_path, B, Hq, Hkv, N, D, seed, group)
+    q, k, v, dO, bq = O.seeded_inputs(seed, (B, Hq, N, D), (B, Hkv, N, D), BF16, n_extra_q=2)
+    bk, bv = O.seeded_inputs(seed + 1000, (B, Hq, N, D), (B, Hkv, N, D), BF16)[1:]
+    geom = dict(is_causal=True, window_size=0, q_offset=0, k_offset=0, scale=None)
+    c = lambda t: t.cuda()
+    out, lse = ops.attention_forward(c(q), c(k), c(v), **geom)
+    dQ, dK, dV, delta, pk = ops.attention_first_backward(c(q), c(k), c(v), out, lse, c(dO), **geom)
+    Qb, Kb, Vb, dOb = ops.attention_second_backward(c(q), c(k), c(v), out, lse, delta, pk, c(dO), dQ, c(bq), c(bk),
+                                                    c(bv), **geom)
+    hs, ks = slice(group * G, group * G + G), slice(group, group + 1)
+    ours = dict(out=out[:1, hs], dQ=dQ[:1, hs], dK=dK[:1, ks], dV=dV[:1, ks], Qbar=Qb[:1, hs], Kbar=Kb[:1, ks],
+                Vbar=Vb[:1, ks], dObar=dOb[:1, hs])
+    ref = O.bob_closed_form(q[:1, hs], k[:1, ks], v[:1, ks], dO[:1, hs], bq[:1, hs], bk[:1, ks], bv[:1, ks], **geom)
+    report = {}
+    for n in O.OUTPUT_NAMES:
+        mo, mt = O.error_metrics(ours[n], getattr(ref, n)), O.error_metrics(theirs[n], getattr(ref, n))
+        report[n] = (mo, mt)
+        # the reference's route is itself sane (otherwise the comparison says nothing)
+        assert mt["l2_rel"] < 1e-2, (n, mt, info.get("torch"), info.get("triton"))
+        assert mo["l2_rel"] <= 1.02 * mt["l2_rel"], (n, mo, mt)
+        assert mo["max_abs_rel"] <= 1.05 * mt["max_abs_rel"], (n, mo, mt)
