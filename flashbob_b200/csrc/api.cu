@@ -224,10 +224,10 @@ static int dispatch_dtype(const bob_sm100_geom* g, SweepParams& prm, const Tenso
                                       : dispatch<MODE, false>(g, prm, tensors, stream, counter_slot);
 }
 
-// Only builds with -DBOB_PHASE_TIMERS (never the shipped library) read a device pointer (hex) from
+// Only builds with -DBOB_PHASE_TIMERS or -DBOB_TRACE (never the shipped library) read a device pointer (hex) from
 // BOB_SM100_PHASE_PTR: 24 cycle counters (12 of a pointwise thread, then 12 of the MMA warp).
 static long long* phase_pointer() {
-#ifdef BOB_PHASE_TIMERS
+#if defined(BOB_PHASE_TIMERS) || defined(BOB_TRACE)
     const char* e = std::getenv("BOB_SM100_PHASE_PTR");
     return e ? reinterpret_cast<long long*>(std::strtoull(e, nullptr, 16)) : nullptr;
 #else

@@ -32,7 +32,16 @@ namespace bob {
 
 // Optional in-kernel phase timers: with -DBOB_PHASE_TIMERS one pointwise thread and the MMA issuer of
 // every CTA add the SM cycles they spend in each phase to SweepParams::phase_cycles[0..15].
-#ifdef BOB_PHASE_TIMERS
+#if defined(BOB_TRACE)
+// Event trace (development builds only): the CTA with blockIdx.x == BOB_TRACE records (event id, SM
+// clock) pairs of one pointwise thread (buffer 0), the MMA warp (buffer 1) and a spare warp that
+// watches barrier completions (buffer 2); SweepParams::phase_cycles points to 3 x 8192 words.
+#define BOB_TR_MAX 8190
+#define BOB_PH_DECL int tr_n = 0;
+#define BOB_TR(buf, i) { if ((buf) < 3 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles && tr_n < BOB_TR_MAX) { p.phase_cycles[(buf) * 8192 + 1 + tr_n] = ((long long)(i) << 48) | (clock64() & 0xFFFFFFFFFFFFLL); ++tr_n; } }
+#define BOB_PH(i) { if ((threadIdx.x & 31) == 0) BOB_TR(tr_role, i) }
+#define BOB_PH_FLUSH(base, on) if ((on) && tr_role < 3 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) p.phase_cycles[tr_role * 8192] = tr_n;
+#elif defined(BOB_PHASE_TIMERS)
 #define BOB_PH_DECL long long ph_t = clock64(); long long ph_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #define BOB_PH(i) { const long long ph_n = clock64(); ph_acc[i] += ph_n - ph_t; ph_t = ph_n; }
 #define BOB_PH_FLUSH(base, on) if ((on) && p.phase_cycles) { for (int ph_i = 0; ph_i < 12; ++ph_i) atomicAdd(reinterpret_cast<unsigned long long*>(p.phase_cycles) + (base) + ph_i, (unsigned long long)ph_acc[ph_i]); }
@@ -559,6 +568,24 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 mbar_wait(bar_full(k % NSTAGE), (k / NSTAGE) & 1);
             if (n_live > 0) mbar_wait(bar_own, (n_live - 1) & 1);
         }
+#ifdef BOB_TRACE
+    } else if (warp == NPW / 32 + 2 && CFG::REBALANCE) {
+        // spare warp: watches the completion of the score products, of the output products (operands
+        // consumed) and of the swept-tile loads, and records when each phase flips
+        if (lane == 0 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) {
+            int tr_n = 0;
+            uint32_t ph_sc = 0, ph_op = 0, ph_full[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const long long t_end = clock64() + 4000000LL;
+            while (clock64() < t_end && tr_n < BOB_TR_MAX - 4) {
+                if (mbar_test_wait(bar_sc_full(0), ph_sc)) { BOB_TR(2, 20) ph_sc ^= 1u; }
+                if (mbar_test_wait(bar_op_empty(0), ph_op)) { BOB_TR(2, 21) ph_op ^= 1u; }
+                #pragma unroll
+                for (int st = 0; st < NSTAGE; ++st)
+                    if (mbar_test_wait(bar_full(st), ph_full[st])) { BOB_TR(2, 30 + st) ph_full[st] ^= 1u; }
+            }
+            p.phase_cycles[2 * 8192] = tr_n;
+        }
+#endif
     } else if (warp == NPW / 32) {
         // =========================== MMA issuer ===============================================
         {
@@ -607,6 +634,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             using NS2 = IntTag<2>;
 
             BOB_PH_DECL
+#ifdef BOB_TRACE
+            constexpr int tr_role = 1;
+#endif
             // scores of the tile with running number `gcnt` (counted over all items of this CTA; group
             // gcnt % NG, that group's tile number gcnt / NG), whose swept tiles sit in pipeline stage
             // `stage` (use number `round`)
@@ -775,6 +805,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         int n_live = 0;                          // items with at least one tile finished so far
         int n_items_done = 0;                    // items finished so far, with or without tiles
         BOB_PH_DECL
+#ifdef BOB_TRACE
+        const int tr_role = (warp == 0) ? 0 : 3;     // only warp 0 records (role 3 is dropped)
+#endif
 
         for (int k_item = 0; ok; ++k_item) {
             const Work wk = follow_ring(k_item);
@@ -1335,9 +1368,15 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     pw_all_phase ^= 1u;
                     store_results = ok && (xch[0] == c_last - c_first);
                     if (store_results) {
+                        // Sum every piece's parked partials, my own included, in the order of the CTAs:
+                        // the result does not depend on which piece happened to finish last.
                         __threadfence();
+                        #pragma unroll
+                        for (int ch = 0; ch < NCH; ++ch) {
+                            #pragma unroll
+                            for (int i = 0; i < 16; ++i) { acc0[ch][i] = 0.f; acc1[ch][i] = 0.f; }
+                        }
                         for (int c = c_first; c <= c_last; ++c) {
-                            if (c == me) continue;
                             const float* other = park_at(c);
                             #pragma unroll
                             for (int ch = 0; ch < NCH; ++ch) {

@@ -42,4 +42,6 @@ def shard(q, k, v, world_size: int, rank: int):
 def from_units(x_units: torch.Tensor, B: int, heads: int) -> torch.Tensor:
     """Inverse of `as_units` for one tensor: [B*Hkv, h, N, D] -> [B, Hkv*h, N, D]."""
     U, h, N, D = x_units.shape
-    return x_units.reshape(B, (U // B) * h, N, D) if heads == (U // B) * h else x_units
+    if B <= 0 or U % B or heads != (U // B) * h:
+        raise ValueError(f"{U} units of {h} heads do not form a [B={B}, H={heads}] tensor")
+    return x_units.reshape(B, heads, N, D)

@@ -32,6 +32,10 @@ def test_unit_views_do_not_copy_and_round_trip():
     assert torch.equal(sharding.from_units(uq, 2, 8), q)
     # unit u = (b, h_kv) holds query heads h_kv*G .. h_kv*G+G-1 of batch b
     assert torch.equal(uq[3], q[1, 4:8])
+    assert torch.equal(sharding.from_units(uk, 2, 2), k)
+    for bad in ((uq, 2, 4), (uq, 3, 8), (uk, 2, 8)):       # head counts / batch sizes that do not match the units
+        with pytest.raises(ValueError):
+            sharding.from_units(*bad)
 
 
 def _free_port():
