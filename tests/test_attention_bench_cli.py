@@ -41,3 +41,23 @@ def test_cli_check_on_gpu(argv):
     (reference: benchmarks/reproduce.sh:52-61), all eight outputs at atol = rtol = 0.08."""
     rows = ab.run(ab.build_parser().parse_args(argv + ["--warmup", "1", "--iters", "3"]))
     assert all(r["status"] == "ok" for r in rows)
+
+
+def test_sweep_lists_the_reference_cases():
+    """The sweep driver covers the case families of the reference's sweep (reference:
+    benchmarks/reproduce.sh:63-107) and every flag list parses with the CLI's own parser."""
+    from flashbob_b200 import attention_sweep
+
+    full = attention_sweep.cases(full=True)
+    names = [n for n, _, _ in full]
+    assert len(full) == 7 + 2 + 4 + 4 + 4 + 10 + 1
+    for expect in ("mha-d64-n256", "mha-d32-n4096", "mha-d128-n4096", "mha-d64-n262144", "mha-d128-n65536", "gqa-n4096",
+                   "mqa-n256", "rectangular"):
+        assert expect in names
+    parser = ab.build_parser()
+    for _, flags, check in full:
+        args = parser.parse_args(flags + (["--check"] if check else ["--no-check"]))
+        assert args.d in (32, 64, 128)
+    assert not dict((n, c) for n, _, c in full)["mha-d64-n32768"]      # too large to materialize: unchecked
+    subset = [n for n, _, _ in attention_sweep.cases(full=False)]
+    assert set(subset) <= set(names) and "rectangular" in subset
