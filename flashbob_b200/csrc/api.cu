@@ -98,6 +98,12 @@ static int col_sweep_tiles(const bob_sm100_geom* g, long long doff, int own_tile
 // split does not apply (too little work per CTA to pay for the cut items' extra epilogues, or a list
 // too long for 32-bit positions).
 static int even_split_span(const bob_sm100_geom* g, long long doff, int TN, int ctas) {
+#ifndef BOB_EVEN_SPLIT
+    // Off: measured slower than the counter-fed item queue (a span of equally many tile pairs holds very
+    // different numbers of items, and every item costs a prologue and an epilogue).
+    (void)g; (void)doff; (void)TN; (void)ctas;
+    return 0;
+#endif
     const int n_own_tiles = (g->Nk + 127) / 128;
     const long long per_rank = (long long)g->Hkv * g->B, G = g->Hq / g->Hkv;
     long long total = 0;

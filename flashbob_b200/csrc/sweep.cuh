@@ -34,13 +34,13 @@ namespace bob {
 // every CTA add the SM cycles they spend in each phase to SweepParams::phase_cycles[0..15].
 #if defined(BOB_TRACE)
 // Event trace (development builds only): the CTA with blockIdx.x == BOB_TRACE records (event id, SM
-// clock) pairs of one pointwise thread (buffer 0), the MMA warp (buffer 1) and a spare warp that
-// watches barrier completions (buffer 2); SweepParams::phase_cycles points to 3 x 8192 words.
+// clock) pairs of one pointwise thread (buffer 0), the two MMA warps (buffers 1, 2) and a spare warp
+// that watches barrier completions (buffer 3); SweepParams::phase_cycles points to 4 x 8192 words.
 #define BOB_TR_MAX 8190
 #define BOB_PH_DECL int tr_n = 0;
-#define BOB_TR(buf, i) { if ((buf) < 3 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles && tr_n < BOB_TR_MAX) { p.phase_cycles[(buf) * 8192 + 1 + tr_n] = ((long long)(i) << 48) | (clock64() & 0xFFFFFFFFFFFFLL); ++tr_n; } }
+#define BOB_TR(buf, i) { if ((buf) < 4 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles && tr_n < BOB_TR_MAX) { p.phase_cycles[(buf) * 8192 + 1 + tr_n] = ((long long)(i) << 48) | (clock64() & 0xFFFFFFFFFFFFLL); ++tr_n; } }
 #define BOB_PH(i) { if ((threadIdx.x & 31) == 0) BOB_TR(tr_role, i) }
-#define BOB_PH_FLUSH(base, on) if ((on) && tr_role < 3 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) p.phase_cycles[tr_role * 8192] = tr_n;
+#define BOB_PH_FLUSH(base, on) if ((on) && tr_role < 4 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) p.phase_cycles[tr_role * 8192] = tr_n;
 #elif defined(BOB_PHASE_TIMERS)
 #define BOB_PH_DECL long long ph_t = clock64(); long long ph_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #define BOB_PH(i) { const long long ph_n = clock64(); ph_acc[i] += ph_n - ph_t; ph_t = ph_n; }
@@ -136,7 +136,7 @@ struct SweepConfig {
         ((NG == 1 && (MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32) ||
          (NG == 1 && (MODE == kBwd1Row || MODE == kBwd1Col) && CW == 64) ||
          (NG == 2 && MODE == kFwd && CW == 128));
-    static constexpr int NTHREADS = REBALANCE ? 384 : NPW + 64;   // + MMA warp + TMA warp (+ 2 idle warps)
+    static constexpr int NTHREADS = REBALANCE ? 384 : NPW + 96;   // + score-MMA warp + TMA warp + output-MMA warp (+ 1 idle warp)
 #ifndef BOB_REGS_POINTWISE
 #define BOB_REGS_POINTWISE 224
 #define BOB_REGS_ROLE 56
@@ -162,13 +162,15 @@ struct SweepConfig {
     static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
     // as many stages of swept tiles as shared memory allows, between 2 and 6: the TMA latency of a
     // tile (~2 us) hides behind the tiles before it
-    // Row-owned second backward at head dim <= 64: the epilogue's global operands (out, dQ: 16-bit,
-    // 16 KB each; pk: fp32, 32 KB) are copied into shared memory with coalesced asynchronous copies
-    // while the item runs, and the results leave through the same buffers with coalesced stores.
-    // (A thread owns one row of the tile; touching global memory row by row costs one 128-byte line
-    // per lane and instruction.)
+    // Row-owned second backward at head dim <= 64: the epilogue's 16-bit global operands (out, dQ:
+    // 16 KB each) are copied into shared memory with coalesced asynchronous copies while the item
+    // runs, and the results leave through the same buffers with coalesced stores.  (A thread owns one
+    // row of the tile; touching global memory row by row costs one 128-byte line per lane and
+    // instruction.)  The fp32 pk rows are read straight from global memory into registers when the
+    // sweep ends (staging them too would cost the 32 KB that a fourth stage of swept tiles needs, and
+    // with three stages the tensor pipe waited ~400 cycles per tile for the next swept tiles).
     static constexpr bool STAGED_IO = (MODE == kBwd2Row) && DPAD == 64 && NG == 1;
-    static constexpr int IO_BYTES = STAGED_IO ? 64 * 1024 : 0;
+    static constexpr int IO_BYTES = STAGED_IO ? 32 * 1024 : 0;
     static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + 16 * 1024 + IO_BYTES;
     static constexpr int STAGE_ROOM = (232448 - FIXED_BYTES) / OTH_STAGE_BYTES;
     static constexpr int STAGE_MAX = 6;
@@ -282,7 +284,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     auto bar_pw = [&](int g) { return bar_grp0 + 40u * g + 32; };             //   the group's own threads
     const uint32_t bar_ring0 = bar_grp0 + 40u * NG;
     auto bar_item_full = [&](int s) { return bar_ring0 + 8u * s; };           // ring slot announced
-    auto bar_item_empty = [&](int s) { return bar_ring0 + 8u * (CFG::RING + s); };   // ring slot read by every follower
+    auto bar_item_empty = [&](int s) { return bar_ring0 + 8u * (CFG::RING + s); };   // ring slot read by every follower (two MMA warps, the pointwise warps)
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -367,7 +369,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         mbar_init(bar_done, 1);
         mbar_init(bar_pw_all, NPW / 32);
         mbar_init(bar_out_free, NPW / 32);
-        for (int s = 0; s < CFG::RING; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), 1 + NPW / 32); }
+        for (int s = 0; s < CFG::RING; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), 2 + NPW / 32); }
         misc[1] = 0;
         mbar_fence_init();
     }
@@ -569,7 +571,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             if (n_live > 0) mbar_wait(bar_own, (n_live - 1) & 1);
         }
 #ifdef BOB_TRACE
-    } else if (warp == NPW / 32 + 2 && CFG::REBALANCE) {
+    } else if (warp == NPW / 32 + 3 && CFG::REBALANCE) {
         // spare warp: watches the completion of the score products, of the output products (operands
         // consumed) and of the swept-tile loads, and records when each phase flips
         if (lane == 0 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) {
@@ -577,17 +579,22 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             uint32_t ph_sc = 0, ph_op = 0, ph_full[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             const long long t_end = clock64() + 4000000LL;
             while (clock64() < t_end && tr_n < BOB_TR_MAX - 4) {
-                if (mbar_test_wait(bar_sc_full(0), ph_sc)) { BOB_TR(2, 20) ph_sc ^= 1u; }
-                if (mbar_test_wait(bar_op_empty(0), ph_op)) { BOB_TR(2, 21) ph_op ^= 1u; }
+                if (mbar_test_wait(bar_sc_full(0), ph_sc)) { BOB_TR(3, 20) ph_sc ^= 1u; }
+                if (mbar_test_wait(bar_op_empty(0), ph_op)) { BOB_TR(3, 21) ph_op ^= 1u; }
                 #pragma unroll
                 for (int st = 0; st < NSTAGE; ++st)
-                    if (mbar_test_wait(bar_full(st), ph_full[st])) { BOB_TR(2, 30 + st) ph_full[st] ^= 1u; }
+                    if (mbar_test_wait(bar_full(st), ph_full[st])) { BOB_TR(3, 30 + st) ph_full[st] ^= 1u; }
             }
-            p.phase_cycles[2 * 8192] = tr_n;
+            p.phase_cycles[3 * 8192] = tr_n;
         }
 #endif
-    } else if (warp == NPW / 32) {
-        // =========================== MMA issuer ===============================================
+    } else if (warp == NPW / 32 || warp == NPW / 32 + 2) {
+        // =========================== MMA issuers ==============================================
+        // Two warps issue the products, each from one elected lane: warp NPW/32 the score-shaped
+        // ones (as far ahead as the pointwise threads hand score accumulators back), warp NPW/32 + 2
+        // the output-shaped ones (as operands arrive).  The tensor pipe takes whichever is ready;
+        // neither warp's waits and loop overhead delay the other's instructions.
+        const bool score_role = (warp == NPW / 32);
         {
             constexpr uint32_t fmt = BF16 ? kFmtBF16 : kFmtF16;
 
@@ -635,7 +642,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
 
             BOB_PH_DECL
 #ifdef BOB_TRACE
-            constexpr int tr_role = 1;
+            const int tr_role = score_role ? 1 : 2;
 #endif
             // scores of the tile with running number `gcnt` (counted over all items of this CTA; group
             // gcnt % NG, that group's tile number gcnt / NG), whose swept tiles sit in pipeline stage
@@ -675,10 +682,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 return true;
             };
 
-            int cnt = 0;                              // swept tiles issued so far, over all items
+            int cnt = 0;                              // swept tiles handled so far, over all items
             int stage = 0, round = 0;                 // pipeline stage of tile `cnt`, and cnt / NSTAGE
             int n_out0 = 0, n_out1 = 0;               // output rounds issued so far, per pointwise group
-            int n_live = 0;                           // items with at least one tile finished so far
+            int n_live = 0;                           // items with at least one tile handled so far
             bool ok = true;
             for (int k_item = 0; ok; ++k_item) {
             const Work wk = follow_ring(k_item);
@@ -688,36 +695,19 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             const Item w = decode(item);
             BOB_ITEM_LOCALS(w, wk)
             if (total == 0) continue;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
-            if (!ok) give_up(kStatusTimeoutMma);
-            // Score products run LOOK tiles ahead of the output products.  With two pointwise groups a
-            // group's next scores are best issued as soon as it has read the current ones, while it
-            // still works on them (LOOK = 2, forward); otherwise one tile ahead.
-            constexpr int LOOK = (MODE == kFwd) ? NG : 1;
-            int sc_it = 0, sc_stage = stage, sc_round = round;     // next tile to issue scores for
-            (void)sc_it; (void)sc_stage; (void)sc_round;
-            auto scores_upto = [&](int last) {
-                while (ok && sc_it < total && sc_it <= last) {
-                    ok = issue_scores(cnt + sc_it, sc_stage, sc_round);
-                    ++sc_it;
-                    if (++sc_stage == NSTAGE) { sc_stage = 0; ++sc_round; }
+            if (score_role) {
+                // the item's own tiles have landed (the TMA warp loads them once the previous item's
+                // last products have finished)
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
+                if (!ok) give_up(kStatusTimeoutMma);
+                for (int it = 0; ok && it < total; ++it) {
+                    ok = issue_scores(cnt + it, stage, round);
+                    if (++stage == NSTAGE) { stage = 0; ++round; }
                 }
-            };
-            if constexpr (LOOK == 1) ok = ok && issue_scores(cnt, stage, round);
-            else scores_upto(LOOK - 1);
-            int n_out = 0;                            // output rounds of this item
-            for (int it = 0; ok && it < total; ++it) {
-                int nstage = stage + 1, nround = round;
-                if (nstage == NSTAGE) { nstage = 0; ++nround; }
-                if constexpr (LOOK == 1) {
-                    if (it + 1 < total && !issue_scores(cnt + it + 1, nstage, nround)) { ok = false; break; }
-                } else {
-                    scores_upto(it + LOOK);
-                    if (!ok) break;
-                }
-                const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
-                const bool has_out = true;
-                if (has_out) {
+            } else {
+                int n_out = 0;                        // output rounds of this item
+                for (int it = 0; ok && it < total; ++it) {
+                    const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
                     const int g = (cnt + it) % NG;
                     const uint32_t ob = tmem_oper + g * CFG::OPER_COLS;
                     int& n_out_g = (g == 0) ? n_out0 : n_out1;
@@ -751,15 +741,18 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                         if (has_uq) out_mma(ob, 0, 1, 1, s, true);        // Kbar += dS^T uQ
                         out_mma(ob, 1, 2, 2, s, acc);                       // Vbar += (P*(F-alpha))^T dO
                     }
-                    if (elect_one()) umma_commit(bar_op_empty(g));
+                    // operands consumed; and the swept tiles of this stage are free again (the score
+                    // products that read them finished before these operands could be formed)
+                    if (elect_one()) { umma_commit(bar_op_empty(g)); umma_commit(bar_empty(stage)); }
                     ++n_out;
+                    if (++stage == NSTAGE) { stage = 0; ++round; }
+                    BOB_PH(4)
                 }
-                if (elect_one()) umma_commit(bar_empty(stage));
-                stage = nstage; round = nround;
-                BOB_PH(4)
+                // all products of the item have finished: its own tiles may be replaced, its output
+                // accumulators read
+                if (elect_one()) umma_commit(bar_done);
             }
             cnt += total;
-            if (elect_one()) umma_commit(bar_done);
             ++n_live;
             }   // items
             BOB_PH_FLUSH(12, lane == 0)
@@ -806,7 +799,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         int n_items_done = 0;                    // items finished so far, with or without tiles
         BOB_PH_DECL
 #ifdef BOB_TRACE
-        const int tr_role = (warp == 0) ? 0 : 3;     // only warp 0 records (role 3 is dropped)
+        const int tr_role = (warp == 0) ? 0 : 4;     // only warp 0 records (role 4 is dropped)
 #endif
 
         for (int k_item = 0; ok; ++k_item) {
@@ -865,7 +858,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
         // staged epilogue operands: 16-byte chunk c of row r sits at chunk position c ^ (r & 7) of
         // its 128-byte line, so that both the row-wise and the chunk-wise accesses are conflict-free
-        const uint32_t io_out = sbase + CFG::OFF_IO, io_dq = io_out + 16384, io_pk = io_out + 32768;
+        const uint32_t io_out = sbase + CFG::OFF_IO, io_dq = io_out + 16384;
         const long long tile_row0 = ((long long)batch * p.Hq + head) * p.Nq + own0;   // first row of the contiguous results
         if constexpr (CFG::STAGED_IO) {
             const uint16_t* g_out = static_cast<const uint16_t*>(p.out) + (long long)batch * p.out_sb + (long long)head * p.out_sh + (long long)own0 * p.out_sn;
@@ -878,12 +871,6 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     cp_async16(io_out + off, g_out + (long long)r * p.out_sn + c * 8);
                     cp_async16(io_dq + off, g_dq + (long long)r * p.dQ_sn + c * 8);
                 }
-            }
-            #pragma unroll
-            for (int k = 0; k < 2048 / NPW; ++k) {
-                const int id = tid + NPW * k, r = id >> 4, c = id & 15;
-                if (own0 + r < n_own && c * 4 < p.D)
-                    cp_async16(io_pk + r * 256 + ((c & 8) << 4) + (((c ^ r) & 7) << 4), p.pk + (tile_row0 + r) * p.D + c * 4);
             }
             cp_async_commit();
         }
@@ -1276,6 +1263,20 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 if (grp == 0 && own_ok) p.lse[row_stat] = (l > 0.f) ? (m + log2f(l)) * kLn2 : -INFINITY;
             }
         }
+        // my row's pk columns, on their way while the row sums are combined and the last products finish
+        constexpr int PKN = CFG::STAGED_IO ? DPAD / (NSPLIT * NG) : 1;
+        float pk_pre[PKN];
+        if constexpr (CFG::STAGED_IO) {
+            const int col_pk = (grp * NSPLIT + sp) * PKN;
+            const float4* src = reinterpret_cast<const float4*>(p.pk + (tile_row0 + row) * p.D + col_pk);
+            #pragma unroll
+            for (int i = 0; i < PKN / 4; ++i) {
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (own_ok && col_pk + 4 * i < p.D) t = __ldg(src + i);
+                pk_pre[4 * i] = t.x; pk_pre[4 * i + 1] = t.y; pk_pre[4 * i + 2] = t.z; pk_pre[4 * i + 3] = t.w;
+            }
+        }
+        (void)pk_pre;
         float alpha = 0.f, ecirc = 0.f;
         ok = __all_sync(0xffffffffu, ok);
         if constexpr (MODE == kBwd2Row) {
@@ -1439,12 +1440,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     if constexpr (CFG::STAGED_IO) {
                         const uint32_t sw = row & 7;
                         #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int c = col / 4 + i;                         // 16-byte chunk of the fp32 row
-                            const uint4 t = ld_shared_v4(io_pk + row * 256 + ((c & 8) << 4) + (((c ^ sw) & 7) << 4));
-                            pkv[4 * i] = __uint_as_float(t.x); pkv[4 * i + 1] = __uint_as_float(t.y);
-                            pkv[4 * i + 2] = __uint_as_float(t.z); pkv[4 * i + 3] = __uint_as_float(t.w);
-                        }
+                        for (int i = 0; i < 16; ++i) pkv[i] = pk_pre[c + i];
                         #pragma unroll
                         for (int i = 0; i < 2; ++i) {
                             const uint32_t off = row * 128 + (((col / 8 + i) ^ sw) << 4);
