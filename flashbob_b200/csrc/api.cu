@@ -324,6 +324,10 @@ extern "C" const char* bob_sm100_error_string(int code) {
 
 // Bytes of the even-split area (flags, then parked partials) a stage's column-owned kernel may use.
 static size_t even_split_bytes(const bob_sm100_geom* g) {
+#ifndef BOB_EVEN_SPLIT
+    (void)g;
+    return 0;
+#endif
     const int sms = sm_count(g->device);
     if (sms <= 0 || !col_launch_is_persistent(g, sms)) return 0;
     return even_split_flag_bytes(g) + even_split_park_bytes(sms);

@@ -136,7 +136,12 @@ struct SweepConfig {
         ((NG == 1 && (MODE == kBwd2Row || MODE == kBwd2Col) && CW == 32) ||
          (NG == 1 && (MODE == kBwd1Row || MODE == kBwd1Col) && CW == 64) ||
          (NG == 2 && MODE == kFwd && CW == 128));
-    static constexpr int NTHREADS = REBALANCE ? 384 : NPW + 96;   // + score-MMA warp + TMA warp + output-MMA warp (+ 1 idle warp)
+    // Two MMA-issuing warps (one for the score-shaped products, one for the output-shaped ones) in the
+    // second backward (measured 6-8 % faster at both head dims) and wherever the warpgroup of the role
+    // warps has spare warps anyway; in the first backward one warp issues both kinds (there a third
+    // role warp costs the 512 pointwise threads registers: 0.36 ms against 0.33 ms).
+    static constexpr bool TWO_MMA = REBALANCE || MODE == kBwd2Row || MODE == kBwd2Col;
+    static constexpr int NTHREADS = REBALANCE ? 384 : NPW + (TWO_MMA ? 96 : 64);   // + MMA warp(s) + TMA warp
 #ifndef BOB_REGS_POINTWISE
 #define BOB_REGS_POINTWISE 224
 #define BOB_REGS_ROLE 56
@@ -369,7 +374,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         mbar_init(bar_done, 1);
         mbar_init(bar_pw_all, NPW / 32);
         mbar_init(bar_out_free, NPW / 32);
-        for (int s = 0; s < CFG::RING; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), 2 + NPW / 32); }
+        for (int s = 0; s < CFG::RING; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), (CFG::TWO_MMA ? 2 : 1) + NPW / 32); }
         misc[1] = 0;
         mbar_fence_init();
     }
@@ -588,13 +593,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             p.phase_cycles[3 * 8192] = tr_n;
         }
 #endif
-    } else if (warp == NPW / 32 || warp == NPW / 32 + 2) {
+    } else if (warp == NPW / 32 || (CFG::TWO_MMA && warp == NPW / 32 + 2)) {
         // =========================== MMA issuers ==============================================
         // Two warps issue the products, each from one elected lane: warp NPW/32 the score-shaped
         // ones (as far ahead as the pointwise threads hand score accumulators back), warp NPW/32 + 2
         // the output-shaped ones (as operands arrive).  The tensor pipe takes whichever is ready;
         // neither warp's waits and loop overhead delay the other's instructions.
-        const bool score_role = (warp == NPW / 32);
+        const bool score_role = (warp == NPW / 32);       // (with a single MMA warp: this warp does both)
         {
             constexpr uint32_t fmt = BF16 ? kFmtBF16 : kFmtF16;
 
@@ -695,61 +700,91 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             const Item w = decode(item);
             BOB_ITEM_LOCALS(w, wk)
             if (total == 0) continue;
-            if (score_role) {
-                // the item's own tiles have landed (the TMA warp loads them once the previous item's
-                // last products have finished)
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
-                if (!ok) give_up(kStatusTimeoutMma);
-                for (int it = 0; ok && it < total; ++it) {
-                    ok = issue_scores(cnt + it, stage, round);
-                    if (++stage == NSTAGE) { stage = 0; ++round; }
+            int n_out = 0;                            // output rounds of this item
+            // output products of the item's tile `it`, whose swept tiles sit in pipeline stage `st`
+            auto issue_outputs = [&](int it, int st) -> bool {
+                const uint32_t s = oth16 + ((st * CFG::OTH_STAGE_BYTES) >> 4);
+                const int g = (cnt + it) % NG;
+                const uint32_t ob = tmem_oper + g * CFG::OPER_COLS;
+                int& n_out_g = (g == 0) ? n_out0 : n_out1;
+                BOB_PH(7)
+                if (!__all_sync(0xffffffffu, mbar_wait(bar_op_full(g), n_out_g & 1))) { give_up(kStatusTimeoutMma); return false; }
+                // the first products of an item overwrite the output accumulators: the pointwise
+                // threads must have read out the previous item's
+                if (n_out == 0 && n_live > 0 &&
+                    !__all_sync(0xffffffffu, mbar_wait(bar_out_free, (n_live - 1) & 1))) { give_up(kStatusTimeoutMma); return false; }
+                ++n_out_g;
+                BOB_PH(3)
+                tc_fence_after_sync();
+                const bool acc = n_out > 0;
+                if constexpr (MODE == kFwd) {
+                    out_mma(ob, g, 0, 1, s, n_out >= NG);               // O_g += P V (group g's own accumulator)
+                } else if constexpr (MODE == kBwd1Row) {
+                    out_mma(ob, 0, 0, 0, s, acc);                       // dQ += dS K
+                    if (p.pk) out_mma(ob, 1, 1, 0, s, acc);             // PK += P K
+                } else if constexpr (MODE == kBwd1Col) {
+                    out_mma(ob, 0, 1, 0, s, acc);                       // dK += dS^T Q
+                    out_mma(ob, 1, 0, 1, s, acc);                       // dV += P^T dO
+                } else if constexpr (MODE == kBwd2Row) {
+                    // operands: P, P*F, P*T, dS;  swept: K, uK, V, uV;  outputs: dObar, Omega
+                    if (has_uv) out_mma(ob, 0, 0, 3, s, acc);         // dObar += P uV
+                    out_mma(ob, 0, 1, 2, s, acc || has_uv);           // dObar += (P*F) V
+                    out_mma(ob, 1, 2, 0, s, acc);                       // Omega += (P*T) K
+                    if (has_uk) out_mma(ob, 1, 3, 1, s, true);        // Omega += dS uK
+                } else {
+                    // operands: Sbar^T, dS^T, (P*(F-alpha))^T;  outputs: Kbar, Vbar
+                    out_mma(ob, 0, 0, 0, s, acc);                       // Kbar += Sbar^T Q
+                    if (has_uq) out_mma(ob, 0, 1, 1, s, true);        // Kbar += dS^T uQ
+                    out_mma(ob, 1, 2, 2, s, acc);                       // Vbar += (P*(F-alpha))^T dO
+                }
+                // operands consumed; and the swept tiles of this stage are free again (the score
+                // products that read them finished before these operands could be formed)
+                if (elect_one()) { umma_commit(bar_op_empty(g)); umma_commit(bar_empty(st)); }
+                ++n_out;
+                BOB_PH(4)
+                return true;
+            };
+            if constexpr (CFG::TWO_MMA) {
+                if (score_role) {
+                    // the item's own tiles have landed (the TMA warp loads them once the previous item's
+                    // last products have finished)
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
+                    if (!ok) give_up(kStatusTimeoutMma);
+                    for (int it = 0; ok && it < total; ++it) {
+                        ok = issue_scores(cnt + it, stage, round);
+                        if (++stage == NSTAGE) { stage = 0; ++round; }
+                    }
+                } else {
+                    for (int it = 0; ok && it < total; ++it) {
+                        ok = issue_outputs(it, stage);
+                        if (++stage == NSTAGE) { stage = 0; ++round; }
+                    }
+                    // all products of the item have finished: its own tiles may be replaced, its output
+                    // accumulators read
+                    if (elect_one()) umma_commit(bar_done);
                 }
             } else {
-                int n_out = 0;                        // output rounds of this item
-                for (int it = 0; ok && it < total; ++it) {
-                    const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
-                    const int g = (cnt + it) % NG;
-                    const uint32_t ob = tmem_oper + g * CFG::OPER_COLS;
-                    int& n_out_g = (g == 0) ? n_out0 : n_out1;
-                    BOB_PH(7)
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar_op_full(g), n_out_g & 1))) { give_up(kStatusTimeoutMma); ok = false; break; }
-                    // the first products of an item overwrite the output accumulators: the pointwise
-                    // threads must have read out the previous item's
-                    if (n_out == 0 && n_live > 0 &&
-                        !__all_sync(0xffffffffu, mbar_wait(bar_out_free, (n_live - 1) & 1))) { give_up(kStatusTimeoutMma); ok = false; break; }
-                    ++n_out_g;
-                    BOB_PH(3)
-                    tc_fence_after_sync();
-                    const bool acc = n_out > 0;
-                    if constexpr (MODE == kFwd) {
-                        out_mma(ob, g, 0, 1, s, n_out >= NG);               // O_g += P V (group g's own accumulator)
-                    } else if constexpr (MODE == kBwd1Row) {
-                        out_mma(ob, 0, 0, 0, s, acc);                       // dQ += dS K
-                        if (p.pk) out_mma(ob, 1, 1, 0, s, acc);             // PK += P K
-                    } else if constexpr (MODE == kBwd1Col) {
-                        out_mma(ob, 0, 1, 0, s, acc);                       // dK += dS^T Q
-                        out_mma(ob, 1, 0, 1, s, acc);                       // dV += P^T dO
-                    } else if constexpr (MODE == kBwd2Row) {
-                        // operands: P, P*F, P*T, dS;  swept: K, uK, V, uV;  outputs: dObar, Omega
-                        if (has_uv) out_mma(ob, 0, 0, 3, s, acc);         // dObar += P uV
-                        out_mma(ob, 0, 1, 2, s, acc || has_uv);           // dObar += (P*F) V
-                        out_mma(ob, 1, 2, 0, s, acc);                       // Omega += (P*T) K
-                        if (has_uk) out_mma(ob, 1, 3, 1, s, true);        // Omega += dS uK
-                    } else {
-                        // operands: Sbar^T, dS^T, (P*(F-alpha))^T;  outputs: Kbar, Vbar
-                        out_mma(ob, 0, 0, 0, s, acc);                       // Kbar += Sbar^T Q
-                        if (has_uq) out_mma(ob, 0, 1, 1, s, true);        // Kbar += dS^T uQ
-                        out_mma(ob, 1, 2, 2, s, acc);                       // Vbar += (P*(F-alpha))^T dO
+                // One warp issues both kinds: the score products run LOOK tiles ahead of the output
+                // products (with two pointwise groups a group's next scores are issued as soon as it has
+                // read the current ones; otherwise one tile ahead).
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
+                if (!ok) give_up(kStatusTimeoutMma);
+                constexpr int LOOK = (MODE == kFwd) ? NG : 1;
+                int sc_it = 0, sc_stage = stage, sc_round = round;     // next tile to issue scores for
+                auto scores_upto = [&](int last) {
+                    while (ok && sc_it < total && sc_it <= last) {
+                        ok = issue_scores(cnt + sc_it, sc_stage, sc_round);
+                        ++sc_it;
+                        if (++sc_stage == NSTAGE) { sc_stage = 0; ++sc_round; }
                     }
-                    // operands consumed; and the swept tiles of this stage are free again (the score
-                    // products that read them finished before these operands could be formed)
-                    if (elect_one()) { umma_commit(bar_op_empty(g)); umma_commit(bar_empty(stage)); }
-                    ++n_out;
+                };
+                scores_upto(LOOK - 1);
+                for (int it = 0; ok && it < total; ++it) {
+                    scores_upto(it + LOOK);
+                    if (!ok) break;
+                    ok = issue_outputs(it, stage);
                     if (++stage == NSTAGE) { stage = 0; ++round; }
-                    BOB_PH(4)
                 }
-                // all products of the item have finished: its own tiles may be replaced, its output
-                // accumulators read
                 if (elect_one()) umma_commit(bar_done);
             }
             cnt += total;
