@@ -162,7 +162,19 @@ struct SweepConfig {
     static constexpr int NACC = (MODE == kFwd) ? NG : MT::NOUT;
     static_assert(MODE != kFwd || (NG == 2 && CW == TN && (TN == 64 || TN == 128)), "forward: two groups, one thread per row");
     static constexpr int OUT_COLS = NACC * DPAD;
-    static constexpr int TMEM_NEED = NG * (SC_COLS + OPER_COLS) + OUT_COLS;
+    static constexpr int TMEM_BASE_NEED = NG * (SC_COLS + OPER_COLS) + OUT_COLS;
+    // Second backward: where tensor memory has DPAD / 2 columns to spare, the first own tile (Q, or K
+    // in the column-owned kernel) is also kept there, 16-bit packed like the derived operands, and its
+    // score product reads it from tensor memory: per instruction that product then fetches only the
+    // swept tile from shared memory (measured 47-51 cycles against 69-72 at N = 64, 72 against ~100 at
+    // N = 128).  Fits: column-owned at head dim 64, both kernels at head dim 128.
+#ifdef BOB_OWN_TM
+    static constexpr bool OWN_TM = (MODE == kBwd2Row || MODE == kBwd2Col) && NG == 1 && TMEM_BASE_NEED + DPAD / 2 <= 512;
+#else
+    static constexpr bool OWN_TM = false;
+#endif
+    static constexpr int OWN_TM_COLS = OWN_TM ? DPAD / 2 : 0;
+    static constexpr int TMEM_NEED = TMEM_BASE_NEED + OWN_TM_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
     static_assert(TMEM_NEED <= 512, "tensor memory budget exceeded");
     // as many stages of swept tiles as shared memory allows, between 2 and 6: the TMA latency of a
@@ -188,7 +200,7 @@ struct SweepConfig {
     static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [2][NG * NSPLIT][128] floats
     static constexpr int OFF_BAR = OFF_RED + (MODE == kFwd ? 4 : 2) * NG * NSPLIT * 128 * 4;   // forward: two copies
     static constexpr int RING = 4;                                              // work items announced ahead
-    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG + 2 * RING;
+    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG + 2 * RING + 1;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag, item ring
     static constexpr int OFF_IO = (OFF_MISC + 16 + 32 * RING + 127) & ~127;     // staged epilogue operands
     static constexpr int SMEM_BYTES = OFF_IO + IO_BYTES + 1024;                 // + alignment slack
@@ -289,6 +301,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     auto bar_pw = [&](int g) { return bar_grp0 + 40u * g + 32; };             //   the group's own threads
     const uint32_t bar_ring0 = bar_grp0 + 40u * NG;
     auto bar_item_full = [&](int s) { return bar_ring0 + 8u * s; };           // ring slot announced
+    const uint32_t bar_own_tm = bar_ring0 + 8u * (2 * CFG::RING);                // own tile 0 copied into tensor memory
     auto bar_item_empty = [&](int s) { return bar_ring0 + 8u * (CFG::RING + s); };   // ring slot read by every follower (two MMA warps, the pointwise warps)
 
     const int tid = threadIdx.x;
@@ -375,6 +388,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         mbar_init(bar_pw_all, NPW / 32);
         mbar_init(bar_out_free, NPW / 32);
         for (int s = 0; s < CFG::RING; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), (CFG::TWO_MMA ? 2 : 1) + NPW / 32); }
+        mbar_init(bar_own_tm, NPW / 32);
         misc[1] = 0;
         mbar_fence_init();
     }
@@ -389,6 +403,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     // [scores of group 0 .. NG-1 | operands of group 0 .. NG-1 | output accumulators]
     const uint32_t tmem_oper = tmem + NG * CFG::SC_COLS;
     const uint32_t tmem_out = tmem_oper + NG * CFG::OPER_COLS;
+    const uint32_t tmem_own = tmem_out + CFG::OUT_COLS;                          // own tile 0, packed (OWN_TM only)
+    (void)tmem_own;
 
     auto give_up = [&](int code) {
         misc[1] = 1;
@@ -616,12 +632,14 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 constexpr uint32_t idesc = umma_idesc(fmt, fmt, NS * TN, false);
                 const uint32_t a = own16 + ((slot_a * CFG::OWN_TILE_BYTES) >> 4);
                 const uint32_t b = stage16 + ((slot_b * CFG::OTH_SUB_BYTES) >> 4);
+                const bool from_tm = CFG::OWN_TM && slot_a == 0;          // own tile 0 also sits in tensor memory
                 if (elect_one()) {
                     #pragma unroll
                     for (int ks = 0; ks < DPAD / 16; ++ks) {
                         const uint32_t ao = ((ks / 4) * (128 * 128) + (ks % 4) * 32) >> 4;
                         const uint32_t bo = ((ks / 4) * (MT::NOTH * CFG::OTH_SUB_BYTES) + (ks % 4) * 32) >> 4;
-                        umma_ss_lo(sc_base + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
+                        if (from_tm) umma_ts_lo(sc_base + acc * TN, tmem_own + ks * 8, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
+                        else umma_ss_lo(sc_base + acc * TN, a + ao, b + bo, idesc, (accumulate || ks > 0) ? 1u : 0u);
                     }
                 }
             };
@@ -749,7 +767,9 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     // the item's own tiles have landed (the TMA warp loads them once the previous item's
                     // last products have finished)
                     ok = __all_sync(0xffffffffu, mbar_wait(bar_own, n_live & 1));
+                    if constexpr (CFG::OWN_TM) ok = ok && __all_sync(0xffffffffu, mbar_wait(bar_own_tm, n_live & 1));
                     if (!ok) give_up(kStatusTimeoutMma);
+                    tc_fence_after_sync();
                     for (int it = 0; ok && it < total; ++it) {
                         ok = issue_scores(cnt + it, stage, round);
                         if (++stage == NSTAGE) { stage = 0; ++round; }
@@ -890,6 +910,31 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         }
         if constexpr (MODE == kBwd2Row) {
             if (own_ok) { nL2 = -p.lse[row_stat] * kLog2e; ndlt = -p.delta[row_stat]; }
+        }
+        // Own tile 0 into tensor memory (see SweepConfig::OWN_TM): once the item's own tiles have landed,
+        // every thread copies its share of its own row, 16 elements (two 16-byte chunks of the swizzled
+        // shared-memory tile = eight packed columns) at a time.  The previous item's products are all
+        // finished by now (its epilogue waited for them), so nothing reads the old copy any more.
+        if constexpr (CFG::OWN_TM) {
+            if (total > 0) {
+                ok = pw_wait(bar_own, n_live & 1);
+                if (ok) {
+                    constexpr int PER = (DPAD / 8) / NSPLIT;             // 16-byte chunks of my row that I copy
+                    static_assert(PER % 2 == 0, "two chunks per tensor-memory store");
+                    #pragma unroll
+                    for (int c = sp * PER; c < (sp + 1) * PER; c += 2) {
+                        const uint32_t src = sbase + CFG::OFF_OWN + (c / 8) * (128 * 128);
+                        const uint4 lo = ld_shared_v4(src + sw128_offset(row, c % 8));
+                        const uint4 hi = ld_shared_v4(src + sw128_offset(row, c % 8 + 1));
+                        const uint32_t wds[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                        tmem_st8(tlane + (tmem_own - tmem) + 4 * c, wds);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_own_tm);
+                }
+            }
         }
         // staged epilogue operands: 16-byte chunk c of row r sits at chunk position c ^ (r & 7) of
         // its 128-byte line, so that both the row-wise and the chunk-wise accesses are conflict-free
