@@ -153,11 +153,7 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
     }
     // The second backward has a build of its own for the usual case of three defined tangents.
     constexpr bool kSecond = (MODE == kBwd2Row || MODE == kBwd2Col);
-#ifdef BOB_NO_ALLT
-    const bool allt = false;
-#else
     const bool allt = kSecond && prm.has_uq && prm.has_uk && prm.has_uv;
-#endif
     auto kernel = allt ? sweep_kernel<MODE, DPAD, TN, BF16, NG, CW, kSecond>
                        : sweep_kernel<MODE, DPAD, TN, BF16, NG, CW, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CFG::SMEM_BYTES) !=
@@ -210,11 +206,7 @@ static int dispatch(const bob_sm100_geom* g, SweepParams& prm, const TensorArg* 
                     cudaStream_t stream, int counter_slot) {
     constexpr bool kSecond = (MODE == kBwd2Row || MODE == kBwd2Col);
     if (g->D <= 64) {
-#ifdef BOB_EXP_CW16
-        if constexpr (kSecond)           return launch_sweep<MODE, 64, 64, BF16, 1, 16>(g, prm, tensors, stream, counter_slot);
-#else
         if constexpr (kSecond)           return launch_sweep<MODE, 64, 64, BF16, 1, 32>(g, prm, tensors, stream, counter_slot);
-#endif
         else if constexpr (MODE == kFwd) return launch_sweep<MODE, 64, 128, BF16, 2, 128>(g, prm, tensors, stream, counter_slot);
         else                             return launch_sweep<MODE, 64, 128, BF16, 1, 32>(g, prm, tensors, stream, counter_slot);
     }

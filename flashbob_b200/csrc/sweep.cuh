@@ -167,12 +167,10 @@ struct SweepConfig {
     // in the column-owned kernel) is also kept there, 16-bit packed like the derived operands, and its
     // score product reads it from tensor memory: per instruction that product then fetches only the
     // swept tile from shared memory (measured 47-51 cycles against 69-72 at N = 64, 72 against ~100 at
-    // N = 128).  Fits: column-owned at head dim 64, both kernels at head dim 128.
-#ifdef BOB_OWN_TM
-    static constexpr bool OWN_TM = (MODE == kBwd2Row || MODE == kBwd2Col) && NG == 1 && TMEM_BASE_NEED + DPAD / 2 <= 512;
-#else
-    static constexpr bool OWN_TM = false;
-#endif
+    // N = 128).  Used at head dim 128, where both kernels have the columns (5 % faster); it would also
+    // fit the column-owned kernel at head dim 64, where it measured no gain (0.315 against 0.311 ms:
+    // the next item's score products then wait for the pointwise threads' copy).
+    static constexpr bool OWN_TM = (MODE == kBwd2Row || MODE == kBwd2Col) && NG == 1 && DPAD == 128 && TMEM_BASE_NEED + DPAD / 2 <= 512;
     static constexpr int OWN_TM_COLS = OWN_TM ? DPAD / 2 : 0;
     static constexpr int TMEM_NEED = TMEM_BASE_NEED + OWN_TM_COLS;
     static constexpr int TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
@@ -499,11 +497,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     }
                 }
             } else {
-#ifdef BOB_STATIC_ITEMS
-                if (p.work_counter) wk.item = k_item * (int)gridDim.x + ((k_item & 1) ? ((int)gridDim.x - 1 - (int)blockIdx.x) : (int)blockIdx.x);
-#else
                 if (p.work_counter) { if (lane == 0) wk.item = atomicAdd(p.work_counter, 1); wk.item = __shfl_sync(0xffffffffu, wk.item, 0); }
-#endif
                 else if (k_item == 0) wk.item = (int)blockIdx.x;
                 if (wk.item < 0 || wk.item >= n_items) wk.item = -1;
             }
