@@ -661,12 +661,16 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
 #ifdef BOB_TRACE
             const int tr_role = score_role ? 1 : 2;
 #endif
-            // scores of the tile with running number `gcnt` (counted over all items of this CTA; group
-            // gcnt % NG, that group's tile number gcnt / NG), whose swept tiles sit in pipeline stage
-            // `stage` (use number `round`)
-            auto issue_scores = [&](int gcnt, int stage, int round) -> bool {
+            // scores of an item's tile `it` (pointwise group it % NG: a function of the item alone, so that
+            // which group sums which tiles, and with it the rounding of the result, does not depend on
+            // the items this CTA happened to take before), whose swept tiles sit in pipeline stage
+            // `stage` (use number `round`); j = score rounds issued for that group so far
+            int n_sc0 = 0, n_sc1 = 0;
+            auto issue_scores = [&](int it, int stage, int round) -> bool {
                 const uint32_t s = oth16 + ((stage * CFG::OTH_STAGE_BYTES) >> 4);
-                const int g = gcnt % NG, j = gcnt / NG;
+                const int g = it % NG;
+                int& n_sc_g = (g == 0) ? n_sc0 : n_sc1;
+                const int j = n_sc_g++;
                 const uint32_t sc = tmem + g * CFG::SC_COLS;
                 BOB_PH(7)
                 if (!__all_sync(0xffffffffu, mbar_wait(bar_full(stage), round & 1))) { give_up(kStatusTimeoutMma); return false; }
@@ -716,7 +720,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             // output products of the item's tile `it`, whose swept tiles sit in pipeline stage `st`
             auto issue_outputs = [&](int it, int st) -> bool {
                 const uint32_t s = oth16 + ((st * CFG::OTH_STAGE_BYTES) >> 4);
-                const int g = (cnt + it) % NG;
+                const int g = it % NG;
                 const uint32_t ob = tmem_oper + g * CFG::OPER_COLS;
                 int& n_out_g = (g == 0) ? n_out0 : n_out1;
                 BOB_PH(7)
@@ -765,7 +769,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     if (!ok) give_up(kStatusTimeoutMma);
                     tc_fence_after_sync();
                     for (int it = 0; ok && it < total; ++it) {
-                        ok = issue_scores(cnt + it, stage, round);
+                        ok = issue_scores(it, stage, round);
                         if (++stage == NSTAGE) { stage = 0; ++round; }
                     }
                 } else {
@@ -787,7 +791,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 int sc_it = 0, sc_stage = stage, sc_round = round;     // next tile to issue scores for
                 auto scores_upto = [&](int last) {
                     while (ok && sc_it < total && sc_it <= last) {
-                        ok = issue_scores(cnt + sc_it, sc_stage, sc_round);
+                        ok = issue_scores(sc_it, sc_stage, sc_round);
                         ++sc_it;
                         if (++sc_stage == NSTAGE) { sc_stage = 0; ++sc_round; }
                     }
@@ -951,7 +955,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
 
 
         // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
-        auto tile_body = [&](auto full_tag, int it, int gcnt, int tile, int outer, int stage, int round) -> bool {
+        auto tile_body = [&](auto full_tag, int it, int tile, int outer, int stage, int round) -> bool {
             constexpr bool FULL = decltype(full_tag)::value;
             const int oth0 = tile * TN;
 
@@ -960,7 +964,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 // the swept tile's row statistics were staged by the producer warp
                 if (!pw_wait(bar_stat(stage), round & 1)) return false;
             }
-            if (!pw_wait(bar_sc_full(grp), (gcnt / NG) & 1)) return false;
+            if (!pw_wait(bar_sc_full(grp), n_op & 1)) return false;     // my group's n_op-th tile
             BOB_PH(0)
             tc_fence_after_sync();
 
@@ -1298,11 +1302,11 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             }
             int tile = t_lo + (T > 0 ? lin0 % T : 0), outer = T > 0 ? lin0 / T : 0;
             for (int it = 0; ok && it < total; ++it) {
-                if ((cnt + it) % NG == grp) {            // my group's turn
+                if (it % NG == grp) {                    // my group's turn
                     // is the whole 128 x TN tile pair unmasked and inside both tensors?  (uniform per CTA)
                     const bool full = tile >= full_lo && tile < full_hi;
-                    ok = full ? tile_body(BoolTag<true>{}, it, cnt + it, tile, outer, stage, round)
-                              : tile_body(BoolTag<false>{}, it, cnt + it, tile, outer, stage, round);
+                    ok = full ? tile_body(BoolTag<true>{}, it, tile, outer, stage, round)
+                              : tile_body(BoolTag<false>{}, it, tile, outer, stage, round);
                 }
                 if (++tile == t_hi) { tile = t_lo; ++outer; }
                 if (++stage == NSTAGE) { stage = 0; ++round; }
@@ -1331,9 +1335,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 const float l = a0 * xb[2 * 128 + row] + a1 * xb[3 * 128 + row];
                 const float inv = (l > 0.f) ? 1.f / l : 0.f;
                 // a group that took no tile of this item has never written its accumulator
-                const int first_grp = (cnt - total) % NG;
-                fwd_k0 = (total >= 2 || (total == 1 && first_grp == 0)) ? a0 * inv : 0.f;
-                fwd_k1 = (total >= 2 || (total == 1 && first_grp == 1)) ? a1 * inv : 0.f;
+                fwd_k0 = (total >= 1) ? a0 * inv : 0.f;
+                fwd_k1 = (total >= 2) ? a1 * inv : 0.f;
                 if (grp == 0 && own_ok) p.lse[row_stat] = (l > 0.f) ? (m + log2f(l)) * kLn2 : -INFINITY;
             }
         }

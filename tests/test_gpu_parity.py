@@ -309,3 +309,61 @@ def test_a_give_up_is_visible_without_synchronising_per_call():
         ops.check_device_status()
     assert lib.bob_sm100_last_status(dev) == 0              # reading clears it
     ops.attention_forward(t, t, t, **geom)                  # and later calls are unaffected
+
+
+@pytest.mark.parametrize("shape", [(8, 12, 12, 1024, 64), (1, 32, 8, 2048, 64), (2, 8, 2, 1024, 128)])
+def test_repeated_calls_are_bit_identical(shape):
+    """Every stage returns the same bits for the same inputs, however the work items were dealt to the
+    CTAs of a persistent launch (more items than SMs in the first two shapes): an item is computed by
+    one CTA, and which pointwise group sums which of its tiles depends on the item alone."""
+    B, Hq, Hkv, N, D = shape
+    g = torch.Generator().manual_seed(7)
+    r = lambda h: torch.randn(B, h, N, D, generator=g).to(BF16).cuda()
+    q, k, v, dO, uQ, uK, uV = r(Hq), r(Hkv), r(Hkv), r(Hq), r(Hq), r(Hkv), r(Hkv)
+    geom = _geom(N, N, is_causal=True)
+    first = ops.attention_forward(q, k, v, **geom)
+    for _ in range(4):
+        again = ops.attention_forward(q, k, v, **geom)
+        assert all(torch.equal(a, b) for a, b in zip(first, again))
+    out, lse = first
+    b1 = ops.attention_first_backward(q, k, v, out, lse, dO, **geom)
+    for _ in range(3):
+        again = ops.attention_first_backward(q, k, v, out, lse, dO, **geom)
+        assert all(torch.equal(a, b) for a, b in zip(b1, again))
+    dQ, _, _, delta, pk = b1
+    b2 = ops.attention_second_backward(q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, **geom)
+    for _ in range(3):
+        again = ops.attention_second_backward(q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, **geom)
+        assert all(torch.equal(a, b) for a, b in zip(b2, again))
+
+
+def test_the_three_stages_replay_from_a_cuda_graph():
+    """Launch-bound callers (many small per-layer calls, reference: examples/hessian_vector_product.py:54-61)
+    can record the calls once: after one eager call per device (which creates the library's host-visible
+    status word) the C-ABI entry points only enqueue work on the given stream - a memset of the status
+    block and the kernels - so a stream capture takes them, and a replay returns the eager call's bits."""
+    if ops._CHECK_STATUS:
+        pytest.skip("BOB_SM100_CHECK_STATUS=1 synchronises after every call, which a stream capture forbids")
+    B, Hq, Hkv, N, D = 2, 12, 12, 512, 64
+    g = torch.Generator().manual_seed(11)
+    r = lambda h: torch.randn(B, h, N, D, generator=g).to(BF16).cuda()
+    q, k, v, dO, uQ, uK, uV = r(Hq), r(Hkv), r(Hkv), r(Hq), r(Hq), r(Hkv), r(Hkv)
+    geom = _geom(N, N, is_causal=True)
+
+    def stages():
+        out, lse = ops.attention_forward(q, k, v, **geom)
+        dQ, dK, dV, delta, pk = ops.attention_first_backward(q, k, v, out, lse, dO, **geom)
+        return (out, dQ, dK, dV) + ops.attention_second_backward(q, k, v, out, lse, delta, pk, dO, dQ, uQ, uK, uV, **geom)
+
+    eager = [t.clone() for t in stages()]
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        recorded = stages()
+    for _ in range(2):
+        for t in recorded:
+            t.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert all(torch.equal(a, b) for a, b in zip(recorded, eager))
+    ops.check_device_status()
