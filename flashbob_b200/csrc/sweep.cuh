@@ -181,10 +181,13 @@ struct SweepConfig {
     // 16 KB each) are copied into shared memory with coalesced asynchronous copies while the item
     // runs, and the results leave through the same buffers with coalesced stores.  (A thread owns one
     // row of the tile; touching global memory row by row costs one 128-byte line per lane and
-    // instruction.)  The fp32 pk rows are read straight from global memory into registers when the
-    // sweep ends (staging them too would cost the 32 KB that a fourth stage of swept tiles needs, and
-    // with three stages the tensor pipe waited ~400 cycles per tile for the next swept tiles).
-    static constexpr bool STAGED_IO = (MODE == kBwd2Row) && DPAD == 64 && NG == 1;
+    // instruction.)  Both directions are the work of the fourth warp of the role warpgroup (the "IO
+    // warp"), not of the pointwise threads: between two items the tensor pipe waits for the pointwise
+    // threads, so whatever they do not have to do there is gained.  The fp32 pk rows are read straight
+    // from global memory into registers when the sweep ends (staging them too would cost the 32 KB
+    // that a fourth stage of swept tiles needs, and with three stages the tensor pipe waited ~400
+    // cycles per tile for the next swept tiles).
+    static constexpr bool STAGED_IO = (MODE == kBwd2Row) && DPAD == 64 && NG == 1 && REBALANCE;
     static constexpr int IO_BYTES = STAGED_IO ? 32 * 1024 : 0;
     static constexpr int FIXED_BYTES = MT::NOWN * OWN_TILE_BYTES + 16 * 1024 + IO_BYTES;
     static constexpr int STAGE_ROOM = (232448 - FIXED_BYTES) / OTH_STAGE_BYTES;
@@ -198,7 +201,7 @@ struct SweepConfig {
     static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [2][NG * NSPLIT][128] floats
     static constexpr int OFF_BAR = OFF_RED + (MODE == kFwd ? 4 : 2) * NG * NSPLIT * 128 * 4;   // forward: two copies
     static constexpr int RING = 4;                                              // work items announced ahead
-    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG + 2 * RING + 1;
+    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG + 2 * RING + 1 + 2;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag, item ring
     static constexpr int OFF_IO = (OFF_MISC + 16 + 32 * RING + 127) & ~127;     // staged epilogue operands
     static constexpr int SMEM_BYTES = OFF_IO + IO_BYTES + 1024;                 // + alignment slack
@@ -300,6 +303,8 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     const uint32_t bar_ring0 = bar_grp0 + 40u * NG;
     auto bar_item_full = [&](int s) { return bar_ring0 + 8u * s; };           // ring slot announced
     const uint32_t bar_own_tm = bar_ring0 + 8u * (2 * CFG::RING);                // own tile 0 copied into tensor memory
+    const uint32_t bar_io_full = bar_own_tm + 8;                               // IO warp: the item's out / dQ rows are staged
+    const uint32_t bar_io_ready = bar_own_tm + 16;                             // pointwise warps: the item's results are staged
     auto bar_item_empty = [&](int s) { return bar_ring0 + 8u * (CFG::RING + s); };   // ring slot read by every follower (two MMA warps, the pointwise warps)
 
     const int tid = threadIdx.x;
@@ -385,8 +390,10 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         mbar_init(bar_done, 1);
         mbar_init(bar_pw_all, NPW / 32);
         mbar_init(bar_out_free, NPW / 32);
-        for (int s = 0; s < CFG::RING; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), (CFG::TWO_MMA ? 2 : 1) + NPW / 32); }
+        for (int s = 0; s < CFG::RING; ++s) { mbar_init(bar_item_full(s), 1); mbar_init(bar_item_empty(s), (CFG::TWO_MMA ? 2 : 1) + (CFG::STAGED_IO ? 1 : 0) + NPW / 32); }
         mbar_init(bar_own_tm, NPW / 32);
+        mbar_init(bar_io_full, 1);
+        mbar_init(bar_io_ready, NPW / 32);
         misc[1] = 0;
         mbar_fence_init();
     }
@@ -510,6 +517,25 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             if (item < 0) break;
             const Item w = decode(item);
             BOB_ITEM_LOCALS(w, wk)
+            if constexpr (MODE == kBwd1Row || MODE == kBwd2Row) {
+                // The pointwise threads start the item by reading their rows' statistics (and, in the
+                // first backward, the rows of `out` for delta) with plain loads whose latency nothing
+                // hides: ask for those lines now, a few tiles before they get there.
+                const long long rs0 = ((long long)batch * p.Hq + head) * p.Nq + own0;
+                const int r4 = (lane & 3) * 32;                      // 32 floats per line
+                if (lane < 4 && own0 + r4 < n_own) prefetch_l2(p.lse + rs0 + r4);
+                if (MODE == kBwd2Row && lane >= 4 && lane < 8 && own0 + r4 < n_own) prefetch_l2(p.delta + rs0 + r4);
+                if constexpr (MODE == kBwd1Row) {
+                    const uint16_t* g_out = static_cast<const uint16_t*>(p.out) + (long long)batch * p.out_sb + (long long)head * p.out_sh + (long long)own0 * p.out_sn;
+                    #pragma unroll
+                    for (int r = lane; r < 128; r += 32) {
+                        if (own0 + r < n_own) {
+                            prefetch_l2(g_out + (long long)r * p.out_sn);
+                            if (DPAD > 64 && p.D > 64) prefetch_l2(g_out + (long long)r * p.out_sn + 64);
+                        }
+                    }
+                }
+            }
             if (total == 0) continue;
             if (n_live > 0) {
                 // the previous item's last products have finished reading its own tiles
@@ -584,6 +610,49 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             for (int k = max(0, cnt - NSTAGE); k < cnt; ++k)
                 mbar_wait(bar_full(k % NSTAGE), (k / NSTAGE) & 1);
             if (n_live > 0) mbar_wait(bar_own, (n_live - 1) & 1);
+        }
+    } else if (CFG::STAGED_IO && warp == NPW / 32 + 3) {
+        // =========================== IO warp ==================================================
+        // Per item: copy the tile's `out` and `dQ` rows into the two staging buffers (16-byte chunk c of
+        // row r at chunk position c ^ (r & 7) of its 128-byte line), tell the pointwise threads, wait
+        // until they have replaced them by the results (Qbar over dQ, dObar over out) and write those
+        // out, whole 128-byte lines per quarter warp.
+        const uint32_t io_out = sbase + CFG::OFF_IO, io_dq = io_out + 16384;
+        for (int k_item = 0;; ++k_item) {
+            const Work wk = follow_ring(k_item);
+            if (wk.item == -2) give_up(kStatusTimeoutLoad);
+            if (wk.item < 0) break;
+            const Item w = decode(wk.item);
+            BOB_ITEM_LOCALS(w, wk)
+            const uint16_t* g_out = static_cast<const uint16_t*>(p.out) + (long long)batch * p.out_sb + (long long)head * p.out_sh + (long long)own0 * p.out_sn;
+            const uint16_t* g_dq = static_cast<const uint16_t*>(p.dQ) + (long long)batch * p.dQ_sb + (long long)head * p.dQ_sh + (long long)own0 * p.dQ_sn;
+            #pragma unroll 4
+            for (int k = 0; k < 1024 / 32; ++k) {
+                const int id = lane + 32 * k, r = id >> 3, c = id & 7;
+                if (own0 + r < n_own && c * 8 < p.D) {
+                    const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
+                    cp_async16(io_out + off, g_out + (long long)r * p.out_sn + c * 8);
+                    cp_async16(io_dq + off, g_dq + (long long)r * p.dQ_sn + c * 8);
+                }
+            }
+            cp_async_commit();
+            cp_async_wait_all();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_io_full);
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_io_ready, k_item & 1))) { give_up(kStatusTimeoutLoad); break; }
+            const long long tile_row0 = ((long long)batch * p.Hq + head) * p.Nq + own0;     // results are contiguous
+            uint16_t* g_q = static_cast<uint16_t*>(p.res0) + tile_row0 * p.D;
+            uint16_t* g_do = static_cast<uint16_t*>(p.res1) + tile_row0 * p.D;
+            #pragma unroll 4
+            for (int k = 0; k < 1024 / 32; ++k) {
+                const int id = lane + 32 * k, r = id >> 3, c = id & 7;
+                if (own0 + r < n_own && c * 8 < p.D) {
+                    const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4*>(g_q + (long long)r * p.D + c * 8) = ld_shared_v4(io_dq + off);
+                    *reinterpret_cast<uint4*>(g_do + (long long)r * p.D + c * 8) = ld_shared_v4(io_out + off);
+                }
+            }
+            __syncwarp();
         }
 #ifdef BOB_TRACE
     } else if (warp == NPW / 32 + 3 && CFG::REBALANCE) {
@@ -934,24 +1003,19 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 }
             }
         }
-        // staged epilogue operands: 16-byte chunk c of row r sits at chunk position c ^ (r & 7) of
-        // its 128-byte line, so that both the row-wise and the chunk-wise accesses are conflict-free
+        if constexpr (MODE == kBwd2Row) {
+            // my row's pk columns are read when the sweep ends: have them in L2 by then
+            constexpr int DCP = DPAD / (NSPLIT * NG);            // fp32 columns per thread, 128 bytes per 32
+            const int c0 = (grp * NSPLIT + sp) * DCP;
+            #pragma unroll
+            for (int c = 0; c < DCP; c += 32)
+                if (own_ok && c0 + c < p.D) prefetch_l2(p.pk + (((long long)batch * p.Hq + head) * p.Nq + own_idx) * p.D + c0 + c);
+        }
+        // epilogue operands staged by the IO warp: 16-byte chunk c of row r sits at chunk position
+        // c ^ (r & 7) of its 128-byte line, so that both the row-wise and the chunk-wise accesses are
+        // conflict-free
         const uint32_t io_out = sbase + CFG::OFF_IO, io_dq = io_out + 16384;
         const long long tile_row0 = ((long long)batch * p.Hq + head) * p.Nq + own0;   // first row of the contiguous results
-        if constexpr (CFG::STAGED_IO) {
-            const uint16_t* g_out = static_cast<const uint16_t*>(p.out) + (long long)batch * p.out_sb + (long long)head * p.out_sh + (long long)own0 * p.out_sn;
-            const uint16_t* g_dq = static_cast<const uint16_t*>(p.dQ) + (long long)batch * p.dQ_sb + (long long)head * p.dQ_sh + (long long)own0 * p.dQ_sn;
-            #pragma unroll
-            for (int k = 0; k < 1024 / NPW; ++k) {
-                const int id = tid + NPW * k, r = id >> 3, c = id & 7;
-                if (own0 + r < n_own && c * 8 < p.D) {
-                    const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
-                    cp_async16(io_out + off, g_out + (long long)r * p.out_sn + c * 8);
-                    cp_async16(io_dq + off, g_dq + (long long)r * p.dQ_sn + c * 8);
-                }
-            }
-            cp_async_commit();
-        }
 
 
         // One swept tile.  FULL: every (row, column) of the tile pair is unmasked and in range.
@@ -1360,7 +1424,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             constexpr int NPART = NG * NSPLIT;          // every pointwise thread of my row holds a partial sum
             red_buf[(grp * NSPLIT + sp) * 128 + row] = acc_a.x + acc_a.y;
             red_buf[(NPART + grp * NSPLIT + sp) * 128 + row] = acc_b.x + acc_b.y;
-            if constexpr (CFG::STAGED_IO) cp_async_wait_all();      // my copies; the barrier below publishes them
+            if constexpr (CFG::STAGED_IO) ok = ok && pw_wait(bar_io_full, n_items_done & 1);   // the IO warp has staged out, dQ
             if (ok) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pw_all);
@@ -1562,29 +1626,17 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
             if (total > 0 && !released) release_outputs();   // a thread with no column inside the head dim
         }
         if constexpr (CFG::STAGED_IO) {
-            // every row's results are in shared memory: write the tile out, 16 bytes per thread and
-            // pass, whole 128-byte lines per quarter warp
-            if (ok) ok = pw_sync();
+            // my rows' results are in shared memory: the IO warp writes the tile out (the arrival
+            // publishes my stores; a thread that gave up does not arrive and the IO warp's wait runs out)
             if (ok) {
-                uint16_t* g_q = static_cast<uint16_t*>(p.res0) + tile_row0 * p.D;
-                uint16_t* g_do = static_cast<uint16_t*>(p.res1) + tile_row0 * p.D;
-                #pragma unroll
-                for (int k = 0; k < 1024 / NPW; ++k) {
-                    const int id = tid + NPW * k, r = id >> 3, c = id & 7;
-                    if (own0 + r < n_own && c * 8 < p.D) {
-                        const uint32_t off = r * 128 + ((c ^ (r & 7)) << 4);
-                        *reinterpret_cast<uint4*>(g_q + (long long)r * p.D + c * 8) = ld_shared_v4(io_dq + off);
-                        *reinterpret_cast<uint4*>(g_do + (long long)r * p.D + c * 8) = ld_shared_v4(io_out + off);
-                    }
-                }
-                ok = pw_sync();      // the buffers are free for the next item's copies
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_io_ready);
             }
         }
         if (total > 0) ++n_live;
         ++n_items_done;
         BOB_PH(5)
         }   // items
-        if constexpr (CFG::STAGED_IO) cp_async_wait_all();
         BOB_PH_FLUSH(0, tid == 0)
     }
 #undef BOB_ITEM_LOCALS
