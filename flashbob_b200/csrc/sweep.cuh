@@ -37,10 +37,13 @@ namespace bob {
 // clock) pairs of one pointwise thread (buffer 0), the two MMA warps (buffers 1, 2) and a spare warp
 // that watches barrier completions (buffer 3); SweepParams::phase_cycles points to 4 x 8192 words.
 #define BOB_TR_MAX 8190
+#ifndef BOB_TRACE_MODE
+#define BOB_TRACE_MODE MODE          // -DBOB_TRACE_MODE=<mode>: only that mode's kernel records
+#endif
 #define BOB_PH_DECL int tr_n = 0;
-#define BOB_TR(buf, i) { if ((buf) < 4 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles && tr_n < BOB_TR_MAX) { p.phase_cycles[(buf) * 8192 + 1 + tr_n] = ((long long)(i) << 48) | (clock64() & 0xFFFFFFFFFFFFLL); ++tr_n; } }
+#define BOB_TR(buf, i) { if ((buf) < 4 && MODE == BOB_TRACE_MODE && (int)blockIdx.x == BOB_TRACE && p.phase_cycles && tr_n < BOB_TR_MAX) { p.phase_cycles[(buf) * 8192 + 1 + tr_n] = ((long long)(i) << 48) | (clock64() & 0xFFFFFFFFFFFFLL); ++tr_n; } }
 #define BOB_PH(i) { if ((threadIdx.x & 31) == 0) BOB_TR(tr_role, i) }
-#define BOB_PH_FLUSH(base, on) if ((on) && tr_role < 4 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) p.phase_cycles[tr_role * 8192] = tr_n;
+#define BOB_PH_FLUSH(base, on) if ((on) && tr_role < 4 && MODE == BOB_TRACE_MODE && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) p.phase_cycles[tr_role * 8192] = tr_n;
 #elif defined(BOB_PHASE_TIMERS)
 #define BOB_PH_DECL long long ph_t = clock64(); long long ph_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #define BOB_PH(i) { const long long ph_n = clock64(); ph_acc[i] += ph_n - ph_t; ph_t = ph_n; }
@@ -658,7 +661,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     } else if (warp == NPW / 32 + 3 && CFG::REBALANCE) {
         // spare warp: watches the completion of the score products, of the output products (operands
         // consumed) and of the swept-tile loads, and records when each phase flips
-        if (lane == 0 && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) {
+        if (lane == 0 && MODE == BOB_TRACE_MODE && (int)blockIdx.x == BOB_TRACE && p.phase_cycles) {
             int tr_n = 0;
             uint32_t ph_sc = 0, ph_op = 0, ph_full[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             const long long t_end = clock64() + 4000000LL;
