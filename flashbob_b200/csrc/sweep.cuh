@@ -144,6 +144,13 @@ struct SweepConfig {
     // warps has spare warps anyway; in the first backward one warp issues both kinds (there a third
     // role warp costs the 512 pointwise threads registers: 0.36 ms against 0.33 ms).
     static constexpr bool TWO_MMA = REBALANCE || MODE == kBwd2Row || MODE == kBwd2Col;
+    // Row-owned second backward with all of a tile's columns loaded at once: the score products are
+    // ordered so that S, dP and C are complete before the last product (the second term of F) is
+    // issued, and a barrier of its own tells the pointwise threads, whose loads of those three
+    // accumulators then run under that last product (row-owned kernel 1.6-1.8 % faster; in the column-owned
+    // kernel neither moving uK Q^T to the end nor a barrier before its last product, uV dO^T, paid:
+    // 3-4 % slower).
+    static constexpr bool SPLIT_SC = REBALANCE && MODE == kBwd2Row;
     static constexpr int NTHREADS = REBALANCE ? 384 : NPW + (TWO_MMA ? 96 : 64);   // + MMA warp(s) + TMA warp
 #ifndef BOB_REGS_POINTWISE
 #define BOB_REGS_POINTWISE 224
@@ -204,7 +211,7 @@ struct SweepConfig {
     static constexpr int OFF_RED = OFF_STAT + NSTAGE * 4 * TN * 4;              // [2][NG * NSPLIT][128] floats
     static constexpr int OFF_BAR = OFF_RED + (MODE == kFwd ? 4 : 2) * NG * NSPLIT * 128 * 4;   // forward: two copies
     static constexpr int RING = 4;                                              // work items announced ahead
-    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG + 2 * RING + 1 + 2;
+    static constexpr int NBARS = 1 + 3 * NSTAGE + 3 + 5 * NG + 2 * RING + 1 + 2 + NG;
     static constexpr int OFF_MISC = OFF_BAR + NBARS * 8;                        // tmem slot, abort flag, item ring
     static constexpr int OFF_IO = (OFF_MISC + 16 + 32 * RING + 127) & ~127;     // staged epilogue operands
     static constexpr int SMEM_BYTES = OFF_IO + IO_BYTES + 1024;                 // + alignment slack
@@ -308,6 +315,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
     const uint32_t bar_own_tm = bar_ring0 + 8u * (2 * CFG::RING);                // own tile 0 copied into tensor memory
     const uint32_t bar_io_full = bar_own_tm + 8;                               // IO warp: the item's out / dQ rows are staged
     const uint32_t bar_io_ready = bar_own_tm + 16;                             // pointwise warps: the item's results are staged
+    auto bar_sc_part = [&](int g) { return bar_own_tm + 24 + 8u * g; };        // S, dP, C ready (SPLIT_SC)
     auto bar_item_empty = [&](int s) { return bar_ring0 + 8u * (CFG::RING + s); };   // ring slot read by every follower (two MMA warps, the pointwise warps)
 
     const int tid = threadIdx.x;
@@ -385,6 +393,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
         for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); mbar_init(bar_stat(s), 32); }
         for (int g = 0; g < NG; ++g) {
             mbar_init(bar_sc_full(g), 1);
+            mbar_init(bar_sc_part(g), 1);
             mbar_init(bar_sc_empty(g), GP / 32);
             mbar_init(bar_op_full(g), GP / 32);
             mbar_init(bar_op_empty(g), 1);
@@ -759,9 +768,13 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     // own: Q, dO, uQ;  swept: K, uK, V, uV;  accumulators: S, F, dP, C
                     if (has_uk) score_mma(NS2{}, sc, 0, 0, 0, s, false);      // S | F  = Q [K; uK]^T
                     else          score_mma(NS1{}, sc, 0, 0, 0, s, false);      // S      = Q K^T
-                    if (has_uq) score_mma(NS1{}, sc, 1, 2, 0, s, has_uk);   // F     += uQ K^T
+                    if (!CFG::SPLIT_SC && has_uq) score_mma(NS1{}, sc, 1, 2, 0, s, has_uk);   // F     += uQ K^T
                     if (has_uv) score_mma(NS2{}, sc, 2, 1, 2, s, false);      // dP | C = dO [V; uV]^T
                     else          score_mma(NS1{}, sc, 2, 1, 2, s, false);      // dP     = dO V^T
+                    if constexpr (CFG::SPLIT_SC) {
+                        if (elect_one()) umma_commit(bar_sc_part(g));           // S, dP, C are complete
+                        if (has_uq) score_mma(NS1{}, sc, 1, 2, 0, s, has_uk);   // F     += uQ K^T
+                    }
                 } else {
                     // own: K, V, uK, uV;  swept: Q, uQ, dO;  accumulators: S^T, F^T, dP^T, C^T
                     if (has_uq) score_mma(NS2{}, sc, 0, 0, 0, s, false);      // S^T | F^T = K [Q; uQ]^T
@@ -1031,7 +1044,7 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 // the swept tile's row statistics were staged by the producer warp
                 if (!pw_wait(bar_stat(stage), round & 1)) return false;
             }
-            if (!pw_wait(bar_sc_full(grp), n_op & 1)) return false;     // my group's n_op-th tile
+            if (!pw_wait(CFG::SPLIT_SC ? bar_sc_part(grp) : bar_sc_full(grp), n_op & 1)) return false;     // my group's n_op-th tile
             BOB_PH(0)
             tc_fence_after_sync();
 
@@ -1167,16 +1180,19 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                 const bool has_f = BWD2 && (ALLT || has_uq || has_uk);
                 const bool has_c = BWD2 && (ALLT || has_uv);
                 float in_s[NB][RW], in_dp[NB][RW], in_f[NB][RW], in_c[NB][RW];
-                auto issue_loads = [&](int r, int b) {
+                // part: 0 = every accumulator, 1 = all but F, 2 = F alone
+                auto issue_loads = [&](int r, int b, int part = 0) {
                     const int cb = col0 + RW * r;
                     auto ld = [&](uint32_t addr, float* dst) {
                         if constexpr (RW == 16) tmem_ld16(addr, dst); else tmem_ld8(addr, dst);
                     };
-                    ld(tsc + 0 * TN + cb, in_s[b]);
-                    ld(tsc + (BWD2 ? 2 : 1) * TN + cb, in_dp[b]);
+                    if (part != 2) {
+                        ld(tsc + 0 * TN + cb, in_s[b]);
+                        ld(tsc + (BWD2 ? 2 : 1) * TN + cb, in_dp[b]);
+                    }
                     if constexpr (BWD2) {
-                        if (has_f) ld(tsc + 1 * TN + cb, in_f[b]);
-                        if (has_c) ld(tsc + 3 * TN + cb, in_c[b]);
+                        if (part != 1 && has_f) ld(tsc + 1 * TN + cb, in_f[b]);
+                        if (part != 2 && has_c) ld(tsc + 3 * TN + cb, in_c[b]);
                     }
                 };
                 auto release_scores = [&]() {
@@ -1184,7 +1200,18 @@ sweep_kernel(const __grid_constant__ SweepParams p) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_sc_empty(grp));
                 };
-                if constexpr (LOAD_ALL) {
+                if constexpr (CFG::SPLIT_SC) {
+                    // S, dP and C now; F once its second term has been added (the loads above are on
+                    // their way while that product runs)
+                    #pragma unroll
+                    for (int r = 0; r < R; ++r) issue_loads(r, r, 1);
+                    // (forming the probabilities here as well, while that product runs, measured slower:
+                    // 0.311 against 0.260 ms)
+                    if (!pw_wait(bar_sc_full(grp), n_op & 1)) return false;
+                    tc_fence_after_sync();
+                    #pragma unroll
+                    for (int r = 0; r < R; ++r) issue_loads(r, r, 2);
+                } else if constexpr (LOAD_ALL) {
                     #pragma unroll
                     for (int r = 0; r < R; ++r) issue_loads(r, r);
                 } else {
