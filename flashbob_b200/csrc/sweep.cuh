@@ -153,8 +153,8 @@ struct SweepConfig {
     static constexpr bool SPLIT_SC = REBALANCE && MODE == kBwd2Row;
     static constexpr int NTHREADS = REBALANCE ? 384 : NPW + (TWO_MMA ? 96 : 64);   // + MMA warp(s) + TMA warp
 #ifndef BOB_REGS_POINTWISE
-#define BOB_REGS_POINTWISE 224
-#define BOB_REGS_ROLE 56
+#define BOB_REGS_POINTWISE 208       // measured: 224 / 56 starves the role warps' issue loops (column-owned
+#define BOB_REGS_ROLE 88             // second backward 0.309 ms; 216 / 72: 0.301; 208 / 88: 0.297; 200 / 104: 0.303)
 #endif
     static constexpr int REGS_POINTWISE = BOB_REGS_POINTWISE, REGS_ROLE = BOB_REGS_ROLE;
     static_assert(2 * 128 * REGS_POINTWISE + 128 * REGS_ROLE <= 384 * 168 && REGS_POINTWISE % 8 == 0 && REGS_ROLE % 8 == 0,
