@@ -198,7 +198,7 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
 // group its own online softmax and output accumulator.  First backward: 128-wide tiles, one group of
 // 512 threads (more warps per scheduler measured better than fewer threads holding more columns).
 // Second backward: four score accumulators, four operands and two outputs fill tensor memory at
-// 64-wide tiles; one group of 256 threads holds a whole tile's columns at 224 registers.
+// 64-wide tiles; one group of 256 threads holds a whole tile's columns at 208 registers.
 // Head dim 128.  Forward: 64-wide tiles, two groups, a row per thread.  First backward: 64-wide tiles.
 // Second backward: tensor memory (512 columns) leaves room for 32-wide tiles only.
 template <int MODE, bool BF16>
