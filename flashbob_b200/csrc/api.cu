@@ -120,7 +120,7 @@ static size_t even_split_park_bytes(int ctas) { return (size_t)ctas * 2 * 2 * 12
 
 // Whether a column-owned launch of this geometry is persistent (one CTA per SM taking many items).
 static bool col_launch_is_persistent(const bob_sm100_geom* g, int sms) {
-    return g->D <= 64 && (long long)((g->Nk + 127) / 128) * g->Hkv * g->B > sms;
+    return (long long)((g->Nk + 127) / 128) * g->Hkv * g->B > sms;
 }
 
 struct TensorArg {
@@ -173,10 +173,10 @@ static int launch_sweep(const bob_sm100_geom* g, SweepParams& prm, const TensorA
     if (items > 0x7fffffffLL) return kErrGeom;
     const int sms = sm_count(g->device);
     if (sms <= 0) return kErrDevice;
-    // Measured: one persistent CTA per SM is as fast or slightly faster at head dim <= 64; at head dim
-    // 128 one CTA per item (the hardware's own dynamic placement) is ~4 % faster than the static
-    // alternating assignment, so there the grid covers every item and each CTA runs a single round.
-    const bool persistent = (DPAD == 64) && items > sms;
+    // One persistent CTA per SM whenever there are more items than SMs.  (With the earlier static
+    // assignment of items to CTAs, head dim 128 was ~4 % faster with one CTA per item and the hardware's
+    // own placement; fed from the counter the persistent launch is 0.3-2 % faster there too.)
+    const bool persistent = items > sms;
     dim3 grid((unsigned)(persistent ? sms : items), 1, 1);
     // Persistent CTAs take items, longest first, from a counter in the status block (zeroed with it);
     // column-owned ones with a parking area instead split the item list evenly (see the kernel).
