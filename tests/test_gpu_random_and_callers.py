@@ -73,6 +73,59 @@ def test_random_geometry_matches_oracle(seed):
         assert m["l2_rel"] <= l2_bar or m["max_abs"] <= 0.02 * max(1.0, scale), (n, m, geom, (B, Hq, Hkv, Nq, Nk, D))
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_random_geometry_with_many_work_items(seed):
+    """Shapes with several batch elements and heads, so that most launches have more work items than SMs
+    and run persistently (every head dim the C ABI takes, grouped heads with windows and rectangles
+    included); one (batch, KV group) slice of each is compared with the oracle."""
+    rng = random.Random(99991 + seed)
+    D = rng.choice([16, 32, 48, 64, 80, 96, 128])
+    dtype = rng.choice([BF16, BF16, FP16])
+    Hkv, G, B = rng.choice([2, 4, 6]), rng.choice([1, 2, 4, 8]), rng.choice([2, 4, 6])
+    Nq = rng.randint(130, 720)
+    kind = rng.choice(["square", "square", "window", "rect", "noncausal"])
+    if kind in ("square", "window"):
+        Nk, kw = Nq, dict(is_causal=True)
+        if kind == "window":
+            kw["window_size"] = rng.randint(1, Nq + 5)
+    elif kind == "rect":
+        Nk = rng.randint(130, 800)
+        k_off = rng.choice([0, rng.randint(0, 2000)])
+        kw = dict(is_causal=True, k_offset=k_off, q_offset=k_off + rng.randint(0, max(0, Nk - 1)))
+        if rng.random() < 0.5:
+            kw["window_size"] = rng.randint(1, 300)
+    else:
+        Nk, kw = rng.randint(130, 800), dict(is_causal=False)
+    Hq = Hkv * G
+    q, k, v, dO, uQ = O.seeded_inputs(seed, (B, Hq, Nq, D), (B, Hkv, Nk, D), dtype, n_extra_q=2)
+    uK, uV = O.seeded_inputs(seed + 500, (B, Hq, Nq, D), (B, Hkv, Nk, D), dtype)[1:]
+    causal = kw.get("is_causal", False)
+    geom = dict(is_causal=causal, window_size=kw.get("window_size", 0),
+                q_offset=O.infer_q_offset(Nq, Nk, kw.get("q_offset"), kw.get("k_offset", 0), causal),
+                k_offset=kw.get("k_offset", 0), scale=None)
+    c = lambda t: t.cuda()
+    out, lse = ops.attention_forward(c(q), c(k), c(v), **geom)
+    dQ, dK, dV, delta, pk = ops.attention_first_backward(c(q), c(k), c(v), out, lse, c(dO), **geom)
+    Qb, Kb, Vb, dOb = ops.attention_second_backward(c(q), c(k), c(v), out, lse, delta, pk, c(dO), dQ, c(uQ), c(uK),
+                                                    c(uV), **geom)
+    got = dict(out=out, dQ=dQ, dK=dK, dV=dV, Qbar=Qb, Kbar=Kb, Vbar=Vb, dObar=dOb)
+    b, hk = rng.randrange(B), rng.randrange(Hkv)
+    hs = slice(hk * G, hk * G + G)
+    kv = lambda t: t[b:b + 1, hk:hk + 1]
+    qs = lambda t: t[b:b + 1, hs]
+    ref = O.bob_closed_form(qs(q), kv(k), kv(v), qs(dO), qs(uQ), kv(uK), kv(uV), **geom)
+    l2_bar = 8e-3 if dtype == BF16 else 1.5e-3
+    for n in O.OUTPUT_NAMES:
+        r = getattr(ref, n)
+        g = qs(got[n]) if n in ("out", "dQ", "Qbar", "dObar") else kv(got[n])
+        assert torch.isfinite(got[n].float()).all(), (n, geom)
+        scale = r.abs().max().item()
+        if scale == 0:
+            continue
+        m = O.error_metrics(g, r)
+        assert m["l2_rel"] <= l2_bar or m["max_abs"] <= 0.02 * max(1.0, scale), (n, m, geom, (B, Hq, Hkv, Nq, Nk, D))
+
+
 def test_flash_attn_layout_adapter_reads_bnhd_storage_in_place():
     B, N, Hq, Hkv, D = 2, 200, 4, 2, 64
     g = torch.Generator().manual_seed(5)
